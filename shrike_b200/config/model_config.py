@@ -46,6 +46,7 @@ class RMSNormSpec(PartSpec):
 
     width: int
     eps: float
+    offset: float = 0.0   # added to the stored weight: a design that keeps its weights around zero has 1.0 here
     kind: str = field(init=False, default="rmsnorm")
 
 
@@ -165,7 +166,10 @@ class GatedHeadAttentionSpec(PartSpec):
     position * base^(-2i/dims), the rest pass; `window`: a query sees the `window` latest keys;
     `chunk`: a query at position p sees key j <= p only if floor(p / chunk) = floor(j / chunk), runs
     counted from position 0 of the sequence; `head_gate`: head h's output times sigmoid(Wg x)_h.
-    Keys have `head_dim` elements, values `value_dim`.
+    Keys have `head_dim` elements, values `value_dim`.  `rotation` (a `PairRotationSpec`, instead of
+    `rotary`): the same rotation with the pairing, and the stretch of the frequencies, that it names.
+    `sink`: every head has one learned number whose exponential is added to the softmax's denominator;
+    that share of the weight goes to nothing, and the number enters as it is, without `scale`.
     """
 
     width: int
@@ -182,6 +186,8 @@ class GatedHeadAttentionSpec(PartSpec):
     window: int | None = None
     chunk: int | None = None
     head_gate: bool = False
+    rotation: PartSpec | None = None
+    sink: bool = False
     kind: str = field(init=False, default="gated_head_attention")
 
     def __post_init__(self):
@@ -189,6 +195,10 @@ class GatedHeadAttentionSpec(PartSpec):
             raise ConfigError(f"heads={self.num_heads} is not a multiple of kv_heads={self.num_kv_heads}")
         if self.window is not None and self.chunk is not None:
             raise ConfigError("an attention layer has a window or a chunk, not both")
+        if self.rotary is not None and self.rotation is not None:
+            raise ConfigError("an attention layer has `rotary` or `rotation`, not both")
+        if self.rotation is not None and self.rotation.dims > self.head_dim:
+            raise ConfigError(f"rotation over {self.rotation.dims} dimensions of a head of {self.head_dim}")
         for name in ("window", "chunk"):
             if getattr(self, name) is not None and getattr(self, name) < 1:
                 raise ConfigError(f"attention {name} must be >= 1, got {getattr(self, name)}")
@@ -196,6 +206,91 @@ class GatedHeadAttentionSpec(PartSpec):
             dims = self.rotary[0]
             if isinstance(dims, bool) or not isinstance(dims, int) or dims < 2 or dims % 2 or dims > self.head_dim:
                 raise ConfigError(f"rotary dims must be even and at most the head size {self.head_dim}, got {dims!r}")
+
+
+@dataclass(frozen=True)
+class PairRotationSpec(PartSpec):
+    """A rotation by position of the first `dims` dimensions of a vector: pair i of dims/2 turns by
+    position * f_i, f_i = base^(-2i/dims).  `pairing`: "halves" pairs dimension i with i + dims/2,
+    "neighbours" pairs 2i with 2i + 1.  `stretch` (factor, original, fast, slow), the YaRN rule: with
+    d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)),
+    dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i becomes f_i / factor * r_i +
+    f_i (1 - r_i), and cos and sin are both multiplied by 0.1 ln(factor) + 1."""
+
+    dims: int
+    base: float
+    pairing: str = "halves"
+    stretch: tuple | None = None
+    kind: str = field(init=False, default="pair_rotation")
+
+    def __post_init__(self):
+        if isinstance(self.dims, bool) or not isinstance(self.dims, int) or self.dims < 2 or self.dims % 2:
+            raise ConfigError(f"a rotation needs an even number of dimensions, got {self.dims!r}")
+        if self.pairing not in ("halves", "neighbours"):
+            raise ConfigError(f"rotation pairing {self.pairing!r}; known: halves, neighbours")
+        if not self.base > 1:
+            raise ConfigError(f"a rotation's base must exceed 1, got {self.base}")
+        if self.stretch is not None and (len(self.stretch) != 4 or not self.stretch[0] > 0):
+            raise ConfigError("a rotation's stretch is (factor, original, fast, slow) with a positive factor")
+
+
+@dataclass(frozen=True)
+class RotaryLatentAttentionSpec(PartSpec):
+    """Softmax attention over a cached low-rank latent with a rotated key part that all heads share.
+
+    Per token the cache holds c = RMS(first `latent_rank` rows of Wdkv x) * weight and the last
+    `rotary_dim` rows of Wdkv x, rotated by position (`rotation`, over all `rotary_dim` dimensions).
+    Head h's query is [head_dim plain | rotary_dim rotated]; its score with token j is
+    scale * (q_plain . Wuk_h c_j + q_rotated . r_j), its value Wuv_h c_j.  `window`: a query sees the
+    `window` latest keys, itself included (None: all).  `gate`: "element" multiplies the heads' outputs,
+    side by side, by sigmoid(Wg x) element by element; None: no gate.
+    """
+
+    width: int
+    num_heads: int
+    head_dim: int
+    rotary_dim: int
+    value_dim: int
+    latent_rank: int
+    scale: float
+    eps: float
+    rotation: PartSpec
+    window: int | None = None
+    gate: str | None = "element"
+    kind: str = field(init=False, default="rotary_latent_attention")
+
+    def __post_init__(self):
+        if self.rotation.dims != self.rotary_dim:
+            raise ConfigError(f"the rotated part has {self.rotary_dim} dimensions but its rotation {self.rotation.dims}")
+        if self.window is not None and self.window < 1:
+            raise ConfigError(f"attention window must be >= 1, got {self.window}")
+        if self.gate not in (None, "element"):
+            raise ConfigError(f"latent attention gate {self.gate!r}; known: element")
+
+
+@dataclass(frozen=True)
+class DecayLinearAttentionSpec(PartSpec):
+    """Linear attention with a fixed decay per head: q = act(Wq x), k = act(Wk x), v = act(Wv x);
+    S_t = decay_h S_(t-1) + k_t v_t^T from S = 0, o_t = S_t^T q_t (no scale).  The heads' outputs, side by
+    side, are divided by their common root mean square, scaled by a weight, multiplied by
+    sigmoid(Wg x) and projected.  `decays`: one number in (0, 1] per head.  State and recurrence are 32-bit."""
+
+    width: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    decays: tuple
+    eps: float
+    activation: str = "silu"
+    kind: str = field(init=False, default="decay_linear_attention")
+
+    def __post_init__(self):
+        if len(self.decays) != self.num_heads:
+            raise ConfigError(f"{len(self.decays)} decays for {self.num_heads} heads")
+        if any(isinstance(d, bool) or not isinstance(d, (int, float)) or not 0 < d <= 1 for d in self.decays):
+            raise ConfigError(f"every decay lies in (0, 1], got {list(self.decays)}")
+        if self.activation != "silu":
+            raise ConfigError(f"linear attention activation {self.activation!r}; known: silu")
 
 
 @dataclass(frozen=True)
@@ -300,11 +395,14 @@ class TokenPositionEmbeddingSpec(PartSpec):
 @dataclass(frozen=True)
 class PassEntrySpec(PartSpec):
     """Entering pass t over a run of repeated layers: the embedding's output is added to the residual
-    again (`add_embedding`, every pass but the first) and then a learned vector `step[t]`."""
+    again (`add_embedding`, every pass but the first) and then a learned vector `step[t]`.  `mix`: instead
+    of that sum, every pass (the first too) replaces the residual x by Win [x ; e], e the embedding's
+    output and Win a [width, 2 width] matrix, before `step[t]` is added."""
 
     width: int
     passes: int
     add_embedding: bool = True
+    mix: bool = False
     kind: str = field(init=False, default="pass_entry")
 
 
@@ -316,6 +414,7 @@ class LMHeadSpec(PartSpec):
     width: int
     vocab: int
     tied: bool = False
+    scale: float = 1.0   # every logit is multiplied by this
     kind: str = field(init=False, default="lm_head")
 
 

@@ -102,7 +102,17 @@ struct Params {
   float scale;          //   the plain scale, for the two below
   float softcap;        //   s <- softcap * tanh(s / softcap)
   const float* slopes;  //   s <- s - slopes[head] * (query position - key position)
+  // optional: one learned number per head whose exponential is one more term of the softmax's denominator
+  // (a sink: its share of the weight attends to nothing; taken as it is, without `scale`).  It is added where a row's
+  // sum is final.
+  const float* sinks;
 };
+
+// The sink's term of a row's sum whose exponentials are taken relative to `max_log2` (scores times log2 e).
+// A row that saw no key has the maximum -inf: the term is +inf and the row's output 0, as without a sink.
+__device__ __forceinline__ float sink_term(const float* sinks, int head, float max_log2) {
+  return sinks == nullptr ? 0.f : exp2f(sinks[head] * LOG2E - max_log2);
+}
 
 // A score as the softmax takes it (times log2 e), with the soft cap and the distance bias.  The
 // hyperbolic tangent is 1 - 2 / (exp(2 x) + 1) with the hardware exponential: absolute error
@@ -360,6 +370,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   for (int r = 0; r < 2; ++r) {
     const int t = tile_start + warp * 16 + (lane >> 2) + 8 * r;
     if (t >= q_len) continue;
+    row_sum[r] += sink_term(p.sinks, head, row_max[r]);
     const float inv = row_sum[r] > 0.f ? 1.0f / row_sum[r] : 0.f;
     bf16* dst = p.out + (static_cast<size_t>(start + t) * p.num_heads + head) * D + (lane & 3) * 2;
 #pragma unroll
@@ -736,7 +747,8 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + 8 * r;
     if (row >= rows_here || warp >= SW) continue;
-    const float inv = total_sum[r] > 0.f ? 1.0f / total_sum[r] : 0.f;
+    const float whole = direct ? total_sum[r] + sink_term(p.sinks, head0 + row, row_max[r]) : total_sum[r];
+    const float inv = whole > 0.f ? 1.0f / whole : 0.f;
     const size_t slot = (static_cast<size_t>(seq) * p.num_heads + head0 + row) * p.splits + split;
 #pragma unroll
     for (int i = 0; i < MY_PAIRS; ++i) {
@@ -803,6 +815,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
       }
       if (partials == 1) {
+        sum += sink_term(p.sinks, head0 + row, m);
         p.out[(static_cast<size_t>(start) * p.num_heads + head0 + row) * D + d] =
             __float2bfloat16_rn(sum > 0.f ? total / sum : 0.f);
       } else {
@@ -876,6 +889,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       run_max = m;
       run_sum = sum;
     }
+    run_sum += sink_term(p.sinks, head0 + row, run_max);
     const float inv = run_sum > 0.f ? 1.0f / run_sum : 0.f;
     uint2 packed;
     packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
@@ -919,13 +933,14 @@ SHRIKE_API int shrike_attention_bf16_resident_ctas() {
 // (every launch leaves them zero again).
 // `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
 // softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
-SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_cache, const void* v_cache,
-                                                  const int* block_table, int max_blocks, const int* q_start,
-                                                  const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
-                                                  int page_size, int num_pages, float scale, int window, void* out,
-                                                  int has_single, int has_portions, int max_q_len, int splits,
-                                                  int cluster, float* scratch, int* arrivals, int* status,
-                                                  float softcap, const float* slopes, cudaStream_t stream) {
+// `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
+SHRIKE_API int shrike_paged_attention_bf16_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int* block_table, int max_blocks, const int* q_start,
+                                                 const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                                 int page_size, int num_pages, float scale, int window, void* out,
+                                                 int has_single, int has_portions, int max_q_len, int splits,
+                                                 int cluster, float* scratch, int* arrivals, int* status,
+                                                 float softcap, const float* slopes, const float* sinks, cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
@@ -971,6 +986,7 @@ SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_c
   p.scale = scale;
   p.softcap = softcap > 0.f ? softcap : 0.f;
   p.slopes = slopes;
+  p.sinks = sinks;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * (p.splits / p.cluster) * D : nullptr;
   p.arrivals = arrivals;
@@ -993,6 +1009,19 @@ SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_c
     launch_dependent(portions_kernel, grid, THREADS, PORTIONS_SMEM, stream, p);
   }
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* block_table, int max_blocks, const int* q_start,
+                                                  const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                                  int page_size, int num_pages, float scale, int window, void* out,
+                                                  int has_single, int has_portions, int max_q_len, int splits,
+                                                  int cluster, float* scratch, int* arrivals, int* status,
+                                                  float softcap, const float* slopes, cudaStream_t stream) {
+  return shrike_paged_attention_bf16_sinks(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_seqs,
+                                           num_heads, num_kv_heads, page_size, num_pages, scale, window, out, has_single,
+                                           has_portions, max_q_len, splits, cluster, scratch, arrivals, status, softcap,
+                                           slopes, nullptr, stream);
 }
 
 SHRIKE_API int shrike_paged_attention_bf16(const void* q, const void* k_cache, const void* v_cache,

@@ -55,7 +55,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ ctx_len, const int* __restrict__ seq_of_token,
                                int num_heads, int num_kv_heads, int page_size, int num_pages,
                                float scale, int window, float softcap, const float* __restrict__ slopes,
-                               T* __restrict__ out, int num_tokens) {
+                               const float* __restrict__ sinks, T* __restrict__ out, int num_tokens) {
   __shared__ float q_shared[WARPS][D];
   let_dependents_start();
   wait_for_previous();
@@ -130,6 +130,16 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     }
   }
   T* out_row = out + (static_cast<size_t>(token) * num_heads + head) * D;
+  // a sink: one more term of the denominator whose share of the weight attends to nothing (taken without `scale`).  The maximum moves to the larger
+  // of the two first, so that neither exponential overflows.
+  if (sinks != nullptr) {
+    const float sink = sinks[head];
+    const float top = fmaxf(running_max, sink);
+    const float shrink = expf(running_max - top);
+    running_sum = running_sum * shrink + expf(sink - top);
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] *= shrink;
+  }
   const float inv = running_sum > 0.f ? 1.0f / running_sum : 0.f;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
@@ -140,12 +150,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 
 SHRIKE_API int shrike_attention_head_dim() { return D; }
 
-SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
-                                              const int* block_table, int max_blocks, const int* q_start,
-                                              const int* ctx_len, const int* seq_of_token, int dtype,
-                                              int num_tokens, int num_heads, int num_kv_heads,
-                                              int page_size, int num_pages, float scale, int window,
-                                              float softcap, const float* slopes, void* out, cudaStream_t stream) {
+// `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
+SHRIKE_API int shrike_paged_attention_generic_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                    const int* block_table, int max_blocks, const int* q_start,
+                                                    const int* ctx_len, const int* seq_of_token, int dtype,
+                                                    int num_tokens, int num_heads, int num_kv_heads,
+                                                    int page_size, int num_pages, float scale, int window,
+                                                    float softcap, const float* slopes, const float* sinks, void* out,
+                                                    cudaStream_t stream) {
   if (num_tokens <= 0) return SHRIKE_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0)
     return SHRIKE_BAD_ARGUMENT;
@@ -156,10 +168,21 @@ SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache
   paged_attention_generic_kernel<T><<<static_cast<int>(blocks), WARPS * 32, 0, stream>>>(           \
       static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, q_start, ctx_len, seq_of_token, num_heads, num_kv_heads, page_size,  \
-      num_pages, scale, window, softcap, slopes, static_cast<T*>(out), num_tokens)
+      num_pages, scale, window, softcap, slopes, sinks, static_cast<T*>(out), num_tokens)
   if (dtype == SHRIKE_F32) SHRIKE_ATTN_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_ATTN_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;
 #undef SHRIKE_ATTN_CASE
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int max_blocks, const int* q_start,
+                                              const int* ctx_len, const int* seq_of_token, int dtype,
+                                              int num_tokens, int num_heads, int num_kv_heads,
+                                              int page_size, int num_pages, float scale, int window,
+                                              float softcap, const float* slopes, void* out, cudaStream_t stream) {
+  return shrike_paged_attention_generic_sinks(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, seq_of_token,
+                                              dtype, num_tokens, num_heads, num_kv_heads, page_size, num_pages, scale, window,
+                                              softcap, slopes, nullptr, out, stream);
 }

@@ -127,6 +127,9 @@ struct Args {
   // s <- softcap * tanh(s / softcap); s <- s - slopes[head] * (query position - key position)
   float scale, softcap;
   const float* slopes;
+  // optional: one learned number per head whose exponential is one more term of the softmax's denominator (a sink:
+  // its share of the weight attends to nothing; taken as it is, without `scale`), added where a row's sum is final
+  const float* sinks;
 };
 
 // Which (sequence, query tile) a CTA with work index `work` owns: sequences in order, each with its
@@ -568,6 +571,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       }
     } else if (ok && my_count > 0) {
+      if (args.sinks != nullptr) row_sum += exp2f(args.sinks[head] * LOG2E - row_max);   // the sums are relative to row_max
       const float inv = row_sum > 0.f ? 1.0f / row_sum : 0.f;
       __nv_bfloat16* dst = args.out + (static_cast<size_t>(start + t) * args.num_heads + head) * D;
 #pragma unroll
@@ -637,6 +641,7 @@ combine_portions_kernel(const Args args) {
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) acc[c] += src[c * 32 + lane] * w;
   }
+  if (args.sinks != nullptr) total += exp2f(args.sinks[head] * LOG2E - base);
   const float inv = total > 0.f ? 1.0f / total : 0.f;
   __nv_bfloat16* dst = args.out + token_head * D;
 #pragma unroll
@@ -688,13 +693,14 @@ SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int num_tokens,
 // 8, 16, 32, 64.
 // `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
 // softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
-SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const void* k_cache, const void* v_cache,
+// `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
+SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void* q, const void* k_cache, const void* v_cache,
                                                          const int* block_table, int max_blocks, const int* q_start,
                                                          const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
                                                          int num_kv_heads, int page_size, int num_pages, float scale,
                                                          int window, void* out, int skip_single, int max_q_len, int* status,
                                                          int splits, float* scratch, int portion_tiles,
-                                                         const int* seq_of_token, float softcap, const float* slopes,
+                                                         const int* seq_of_token, float softcap, const float* slopes, const float* sinks,
                                                          cudaStream_t stream) {
   using namespace tcattn;
   if (num_seqs <= 0 || num_tokens <= 0) return SHRIKE_OK;
@@ -738,6 +744,7 @@ SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const vo
   args.scale = scale;
   args.softcap = softcap > 0.f ? softcap : 0.f;
   args.slopes = slopes;
+  args.sinks = sinks;
   args.splits = splits;
   args.num_tokens = num_tokens;
   args.num_seqs = num_seqs;
@@ -752,6 +759,20 @@ SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const vo
     if (err != cudaSuccess) return static_cast<int>(err);
   }
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const void* k_cache, const void* v_cache,
+                                                         const int* block_table, int max_blocks, const int* q_start,
+                                                         const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
+                                                         int num_kv_heads, int page_size, int num_pages, float scale,
+                                                         int window, void* out, int skip_single, int max_q_len, int* status,
+                                                         int splits, float* scratch, int portion_tiles,
+                                                         const int* seq_of_token, float softcap, const float* slopes,
+                                                         cudaStream_t stream) {
+  return shrike_paged_attention_tc_portions_sinks(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_tokens,
+                                                  num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window, out,
+                                                  skip_single, max_q_len, status, splits, scratch, portion_tiles, seq_of_token,
+                                                  softcap, slopes, nullptr, stream);
 }
 
 SHRIKE_API int shrike_paged_attention_tc_portions(const void* q, const void* k_cache, const void* v_cache,
@@ -781,6 +802,12 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void*, const void*, cons
 SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void*, const void*, const void*, const int*, int, const int*,
                                                          const int*, int, int, int, int, int, int, float, int, void*, int, int,
                                                          int*, int, float*, int, const int*, float, const float*, cudaStream_t) {
+  return SHRIKE_BAD_ARGUMENT;
+}
+SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void*, const void*, const void*, const int*, int, const int*,
+                                                        const int*, int, int, int, int, int, int, float, int, void*, int, int,
+                                                        int*, int, float*, int, const int*, float, const float*, const float*,
+                                                        cudaStream_t) {
   return SHRIKE_BAD_ARGUMENT;
 }
 

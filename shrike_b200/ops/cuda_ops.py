@@ -118,6 +118,7 @@ class CudaOps:
         self._portion_scratch = None   # partial rows of the portions kernel when a query tile's keys are split
         self._portion_tiles = None
         self._memory_scratch = None   # what the matrix memory's chunk kernels hand from one launch to the next
+        self._decay_scratch = None    # the same for the decayed linear attention: a state per run of tokens
         self.portion_splits = 0  # 0: the kernel library's rule; n: that many key splits for portions (tests)
         self.generation = 0      # grows when the scratch moves
         self._held_stream = None
@@ -156,6 +157,14 @@ class CudaOps:
         lib.shrike_act_mul_blocks.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P]
         lib.shrike_matrix_memory_chunks.argtypes = [_I, _I]
         lib.shrike_matrix_memory_chunks.restype = _LL
+        lib.shrike_decay_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P] + [_I] * 9 + [_P, _P]
+        lib.shrike_decay_scan_chunks.argtypes = [_I, _I]
+        lib.shrike_decay_scan_chunks.restype = _LL
+        lib.shrike_norm_gate.argtypes = [_P, _P, _I, _LL, _I, _I, _P, _F, _P, _I, _I, _I, _P]
+        lib.shrike_latent_rope_store.argtypes = [_P, _I, _LL, _I, _P, _F, _P, _P, _F, _P, _P, _P] + [_I] * 6 + [_LL, _P]
+        lib.shrike_concat_cast.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P]
+        for name in ("shrike_decay_scan", "shrike_norm_gate", "shrike_latent_rope_store", "shrike_concat_cast"):
+            getattr(lib, name).restype = _I
         for name in ("shrike_embed_scaled", "shrike_act_mul_limit", "shrike_tanh_norm", "shrike_head_prep",
                      "shrike_matrix_memory_scan", "shrike_matrix_memory_out", "shrike_route_top", "shrike_act_mul_blocks"):
             getattr(lib, name).restype = _I
@@ -175,6 +184,10 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _P]
             )
             lib.shrike_paged_attention_generic.restype = _I
+            lib.shrike_paged_attention_generic_sinks.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _P, _P]
+            )
+            lib.shrike_paged_attention_generic_sinks.restype = _I
             if head_dim <= build.TENSOR_CORE_HEAD_DIM:
                 self._declare_tensor_core_attention(lib)
             self._attention[head_dim] = lib
@@ -190,6 +203,10 @@ class CudaOps:
             [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P]
         )
         lib.shrike_paged_attention_bf16_scores.restype = _I
+        lib.shrike_paged_attention_bf16_sinks.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P, _P]
+        )
+        lib.shrike_paged_attention_bf16_sinks.restype = _I
         lib.shrike_attention_single_token_pages.argtypes = [_I]
         lib.shrike_attention_single_token_pages.restype = None
         lib.shrike_attention_bf16_resident_ctas.restype = _I
@@ -202,6 +219,10 @@ class CudaOps:
             [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P]
         )
         lib.shrike_paged_attention_tc_portions_scores.restype = _I
+        lib.shrike_paged_attention_tc_portions_sinks.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P, _P]
+        )
+        lib.shrike_paged_attention_tc_portions_sinks.restype = _I
         lib.shrike_attention_tc_portions_rows.restype = _I
         lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
         lib.shrike_attention_tc_portions_splits.restype = _I
@@ -488,7 +509,8 @@ class CudaOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None,
+                        sinks=None):
         """Attention of the batch's new tokens over the paged cache.  `window`: a query sees the `window`
         latest keys.  `chunk` (instead of a window): a query at position p sees key j <= p only when
         floor(p / chunk) = floor(j / chunk).  `max_q_len` and
@@ -496,8 +518,13 @@ class CudaOps:
         entry's length (host list), lets the portions kernel launch exactly the CTAs it needs.
         `softcap` (a positive number) and `slopes` (float32 [num_heads]) change a score
         s = scale * q.k, in this order: s <- softcap * tanh(s / softcap), then
-        s <- s - slopes[head] * (query position - key position)."""
+        s <- s - slopes[head] * (query position - key position).  `sinks` (float32 [num_heads]): exp(sinks[head])
+        is one more term of every softmax's denominator: a weight that goes to nothing (the raw number, without `scale`)."""
         _dense(q, self.dtype, "q")
+        if sinks is not None:
+            _dense(sinks, torch.float32, "softmax sinks")
+            if sinks.numel() != num_heads:
+                raise KernelError("one softmax sink per query head")
         _dense(keys, self.dtype, "key cache")
         _dense(values, self.dtype, "value cache")
         _dense(block_table, torch.int32, "block table")
@@ -512,10 +539,10 @@ class CudaOps:
             window = -int(chunk)   # the kernels' one number: > 0 a window, < 0 runs of that many positions
         if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM:
             self.launches += 1
-            _check(lib.shrike_paged_attention_generic(
+            _check(lib.shrike_paged_attention_generic_sinks(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),
                 _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
-                page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(out), self._stream()),
+                page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(sinks), _ptr(out), self._stream()),
                 "paged_attention")
             return
         if slopes is not None:
@@ -527,20 +554,20 @@ class CudaOps:
         self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
         if plan.tc_portions:
-            _check(lib.shrike_paged_attention_tc_portions_scores(
+            _check(lib.shrike_paged_attention_tc_portions_sinks(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
                 plan.has_single, max_q_len, _ptr(self.status), plan.portion_splits, _ptr(plan.portion_scratch),
                 self.portion_tiles(q_lens, plan.has_single, lib.shrike_attention_tc_portions_rows()), _ptr(seq_of_token),
-                softcap or 0.0, _ptr(slopes), self._stream()), "paged_attention_tc_portions")
+                softcap or 0.0, _ptr(slopes), _ptr(sinks), self._stream()), "paged_attention_tc_portions")
             has_portions = 0
             if not plan.has_single:
                 return
-        _check(lib.shrike_paged_attention_bf16_scores(
+        _check(lib.shrike_paged_attention_bf16_sinks(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
             plan.has_single, has_portions, max_q_len, plan.splits, plan.cluster, _ptr(plan.scratch), _ptr(plan.arrivals),
-            _ptr(self.status), softcap or 0.0, _ptr(slopes), self._stream()),
+            _ptr(self.status), softcap or 0.0, _ptr(slopes), _ptr(sinks), self._stream()),
             "paged_attention_bf16")
 
     def portion_tiles(self, q_lens, skip_single, rows) -> int:
@@ -767,6 +794,115 @@ class CudaOps:
         _check(self.core.shrike_matrix_memory_out(
             _ptr(numerator), _ptr(denominator), _ptr(fused), partials, stride, total, 2 * num_heads * dim + num_heads * vdim,
             _ptr(weight), eps, _ptr(out), self.code, n, num_heads, vdim, self._stream()), "matrix_memory_out")
+
+    DECAY_CHUNK_FROM = 32   # a sequence that brings at least this many tokens runs its decayed scan over runs of tokens
+
+    def decay_scan(self, fused, decays, state, q_start, state_slot, out, num_seqs, num_heads, dim, vdim, longest=0):
+        """Linear attention with a decay per head over the batch's new tokens: S <- decays[h] S + k v^T, o = S^T q, with
+        q (H dim) | k (H dim) | v (H vdim) the SiLU of the first columns of `fused` ([N, total] float32 or a K-split
+        stack).  `state` float32 [slots, H, at least dim * vdim] is read and left updated for the slots `state_slot`
+        names (-1: the sequence is skipped); `out` float32 [N, H * vdim].  `longest`: the most new tokens a sequence
+        of the batch brings (the batch's shape, known on the host); long portions run as products over 64 tokens at a
+        time, short ones and single tokens as a walk, with the same result up to the order of the sums."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(state, torch.float32, "state")
+        _dense(out, torch.float32, "scan output")
+        _dense(decays, torch.float32, "decays")
+        partials, stride = self._stack(fused)
+        total, n = fused.shape[-1], fused.shape[-2]
+        if state.dim() != 3 or state.shape[1] != num_heads or state.shape[2] < dim * vdim or decays.numel() != num_heads:
+            raise KernelError(f"state {tuple(state.shape)} does not fit {num_heads} heads of {dim} x {vdim}")
+        chunk_state = None
+        if longest >= self.DECAY_CHUNK_FROM:
+            need = self.core.shrike_decay_scan_chunks(n, num_seqs) * num_heads * dim * vdim
+            held = self._decay_scratch
+            if held is None or held.numel() < need:
+                held = torch.empty(max(2 * need, 1024), dtype=torch.float32, device=self.device)
+                self._decay_scratch = held
+                self.generation += 1
+            chunk_state = held
+        self.launches += 4 if chunk_state is not None else 1
+        _check(self.core.shrike_decay_scan(
+            _ptr(fused), partials, stride, total, _ptr(decays), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(out),
+            num_seqs, num_heads, dim, vdim, state.shape[0], state.shape[2], int(longest), self.DECAY_CHUNK_FROM, n,
+            _ptr(chunk_state), self._stream()), "decay_scan")
+
+    def norm_gate(self, x, gate_source, gate_at, weight, eps, out):
+        """out = x (float32 [N, W]), each row over its root mean square times `weight` (float32 [W]; None: the row as it
+        is), times the sigmoid of columns `gate_at` .. `gate_at` + W of `gate_source` ([N, total] float32 or a K-split
+        stack; None: no gate), in the type of `out`."""
+        _dense(x, torch.float32, "rows")
+        _dense(out, self.dtype, "gated rows")
+        n, width = x.shape
+        partials, stride, row_width = 1, 0, 0
+        if gate_source is not None:
+            _dense(gate_source, torch.float32, "fused projection")
+            partials, stride = self._stack(gate_source)
+            row_width = gate_source.shape[-1]
+            if gate_at + width > row_width:
+                raise KernelError("the gate's columns lie outside the fused projection")
+        self.launches += 1
+        _check(self.core.shrike_norm_gate(_ptr(x), _ptr(gate_source), partials, stride, row_width, gate_at, _ptr(weight), eps,
+                                          _ptr(out), self.code, n, width, self._stream()), "norm_gate")
+
+    def latent_rope_store(self, fused, latent_weight, eps, positions, inv_freq, gain, q_out, latents, slots, heads, rank,
+                          rot, padded):
+        """A fused projection ([N, total] float32 or a K-split stack) whose row is `heads` x [rank | rot] queries and then
+        [rank | rot] of the token itself, made ready for attention over a cached latent: every [rot] part rotated,
+        dimension i with i + rot/2, by position * inv_freq[i] with cos and sin times `gain`; the token's [rank] part
+        divided by its root mean square and scaled by `latent_weight`.  Queries go to `q_out` [N, heads * padded], the
+        token's [rank | rot] into its page row (`latents`, rows of `padded`; None: not stored); padding is zeroed."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(q_out, self.dtype, "q")
+        partials, stride = self._stack(fused)
+        num_slots = 0
+        if latents is not None:
+            _dense(latents, self.dtype, "latent cache")
+            num_slots = latents.shape[0] * latents.shape[1]
+        self.launches += 1
+        _check(self.core.shrike_latent_rope_store(
+            _ptr(fused), partials, stride, fused.shape[-1], _ptr(latent_weight), eps, _ptr(positions), _ptr(inv_freq),
+            float(gain), _ptr(q_out), _ptr(latents), _ptr(slots), self.code, fused.shape[-2], heads, rank, rot, padded,
+            num_slots, self._stream()), "latent_rope_store")
+
+    def concat_cast(self, resid, terms, other, out):
+        """resid (float32 [N, W]) += the pending `terms` ((tensor, scale), each float32 [N, W] or a K-split stack); then
+        out[N, 2 W] = [resid | other] in the type of `out` (`other` float32 [N, W])."""
+        _dense(resid, torch.float32, "residual")
+        _dense(other, torch.float32, "second half")
+        _dense(out, self.dtype, "joined rows")
+        terms = list(terms)
+        n, width = resid.shape
+        while len(terms) > 4:   # more pending sums than one launch adds: the first ones go into the residual alone
+            self.tanh_norm(resid, terms[:4])
+            terms = terms[4:]
+        count = len(terms)
+        data, parts = (ctypes.c_void_p * 4)(), (ctypes.c_int * 4)()
+        strides, scales = (ctypes.c_longlong * 4)(), (ctypes.c_float * 4)()
+        for index, (tensor, scale) in enumerate(terms):
+            _dense(tensor, torch.float32, "pending sum")
+            data[index] = tensor.data_ptr()
+            parts[index], strides[index] = self._stack(tensor)
+            scales[index] = float(scale)
+        self.launches += 1
+        _check(self.core.shrike_concat_cast(_ptr(resid), data, parts, strides, scales, count, _ptr(other), _ptr(out), self.code,
+                                            n, width, self._stream()), "concat_cast")
+
+    def head_linear(self, x, w, out, heads):
+        """out[n, h, :] = w[h] x[n, h, :]: x [N, heads * P] in the engine's type, w [heads, V, P], out float32
+        [N, heads * V].  One batched library product over the heads, reading and writing in place through strides."""
+        n = x.shape[0]
+        _dense(x, self.dtype, "head inputs")
+        _dense(out, torch.float32, "head outputs")
+        if w.dim() != 3 or w.shape[0] != heads or x.shape[1] != heads * w.shape[2] or out.shape[1] != heads * w.shape[1]:
+            raise KernelError(f"head_linear: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+        self.library_calls += 1
+        a = x.view(n, heads, w.shape[2]).transpose(0, 1)          # [heads, N, P]
+        target = out.view(n, heads, w.shape[1]).transpose(0, 1)   # [heads, N, V]
+        if self.dtype == torch.float32:
+            torch.bmm(a, w.transpose(1, 2), out=target)
+        else:
+            torch.bmm(a, w.transpose(1, 2), out_dtype=torch.float32, out=target)
 
     def route_top(self, x, router, shared_gate, weights, top, renorm_eps):
         """weights [N, E (+ 1)] float32: softmax(router x) over all E experts in 32-bit, the `top` largest

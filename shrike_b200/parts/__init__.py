@@ -1,6 +1,6 @@
 """Parts a layer is put together from.  Importing the package registers the built-in ones."""
 
-from . import attention, block, embedding, experts, latent_attention, matrix_memory, mlp, norm, parallel, rotary  # noqa: F401
+from . import attention, block, embedding, experts, latent_attention, linear_attention, matrix_memory, mlp, norm, parallel, rotary  # noqa: F401
 from .base import (  # noqa: F401
     BLOCKS,
     EMBEDDINGS,

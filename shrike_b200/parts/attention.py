@@ -16,8 +16,9 @@ a query temperature that grows with the logarithm of the position, scores soft-c
 by distance, a key window.  Each of these is a parameter of its spec.
 
 `GatedHeadAttention` adds, each as an option of its spec: a norm of q and k per head, a rotation of
-part of each head, chunks of positions in place of a window, keys and values of different sizes and a
-sigmoid gate per head on the output.
+part of each head (in either pairing, with stretched frequencies), chunks of positions in place of a
+window, keys and values of different sizes, a sigmoid gate per head on the output, and a learned
+sink per head in the softmax's denominator.
 """
 
 from __future__ import annotations
@@ -25,6 +26,7 @@ from __future__ import annotations
 import torch
 
 from .base import KVNeed, ParamSpec, part_class, register_part
+from .rotary import PairRotation
 
 
 class PagedAttention:
@@ -217,6 +219,8 @@ class GatedHeadAttention:
             params["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm")
         if spec.head_gate:
             params["gate.weight"] = ParamSpec((spec.num_heads, spec.width), "matrix")
+        if getattr(spec, "sink", False):
+            params["sink"] = ParamSpec((spec.num_heads,), "sink")
         return params
 
     @staticmethod
@@ -227,6 +231,16 @@ class GatedHeadAttention:
         self.spec, self.ops, self.runtime = spec, ops, runtime
         self.padded = padded_head(max(spec.head_dim, spec.value_dim))
         ops.check_head_dim(self.padded)
+        rotation = None
+        if getattr(spec, "rotation", None) is not None:
+            # the kernel pairs dimension i with i + dims/2: another pairing, and a factor on cos and sin,
+            # become a reordering and a scaling of the q and k rows (weights and biases alike)
+            rotation = PairRotation(spec.rotation, runtime.device)
+            for name, heads in (("q_proj", spec.num_heads), ("k_proj", spec.num_kv_heads)):
+                for kind in ("weight", "bias") if spec.qkv_bias else ("weight",):
+                    tensors[f"{name}.{kind}"] = rotation.arrange_rows(tensors[f"{name}.{kind}"], heads, spec.head_dim)
+            if spec.qk_norm and rotation.order != list(range(spec.rotation.dims)):
+                raise NotImplementedError("a per-head norm weight with neighbours paired: the weight is not reordered")
         rows = [tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight"), tensors.pop("v_proj.weight")]
         if spec.head_gate:
             rows.append(tensors.pop("gate.weight").to(rows[0].dtype))
@@ -257,6 +271,9 @@ class GatedHeadAttention:
             dims, base = spec.rotary
             table = torch.tensor([float(base) ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
             self.inv_freq, self.rot = table.to(torch.float32).to(runtime.device), int(dims)
+        if rotation is not None:
+            self.inv_freq, self.rot = rotation.inv_freq, int(spec.rotation.dims)
+        self.sinks = tensors.pop("sink").to(torch.float32).contiguous() if getattr(spec, "sink", False) else None
         self.out_width = spec.num_heads * self.padded
 
     def forward(self, x, ctx, run):
@@ -279,6 +296,7 @@ class GatedHeadAttention:
             spec.num_heads, spec.num_kv_heads, self.padded, spec.scale, spec.window, attn,
             max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
             **({"chunk": spec.chunk} if spec.chunk is not None else {}),
+            **({"sinks": self.sinks} if self.sinks is not None else {}),
         )
         if gate is not None:
             ops.head_scale(attn, gate, spec.num_heads, self.padded)

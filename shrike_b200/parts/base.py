@@ -62,7 +62,8 @@ from dataclasses import dataclass
 class ParamSpec:
     """A tensor a part expects: its shape and how random weights fill it.
 
-    init: "matrix" | "table" (N(0, 0.02)), "bias" (N(0, 0.02)), "norm" (1 + N(0, 0.1)).
+    init: "matrix" | "table" (N(0, 0.02)), "bias" (N(0, 0.02)), "norm" (1 + N(0, 0.1)),
+    "around_zero" (N(0, 0.1)), "sink" (N(0, 1)), "mix" ([W, 2 W]: identity | 0, plus N(0, 0.02)).
     """
 
     shape: tuple[int, ...]

@@ -9,7 +9,7 @@ branches read x itself; the feed-forward may be absent.  The residual sum is 32-
 gets the rounded residual a branch reads from the kernel that made the sum.
 
 `PreNormBlock`: pre-norm residual block: x += mixer(norm(x)); x += ffn(norm(x))
-(shrike/models/qwen.py:147-150).  The residual `resid` is float32; a branch output
+(shrike/models/qwen.py:147-150); the feed-forward may be absent.  The residual `resid` is float32; a branch output
 is handed on as `delta` and added by the next norm kernel.
 
 When the kernels offer a native issue of whole layers (`ops.layer_program()`) and the four parts
@@ -24,7 +24,9 @@ from .base import PendingSum, register_part
 class PreNormBlock:
     capture_safe = True   # forward() launches the same kernels for the same batch shape, whatever the positions
 
-    def __init__(self, mixer, mixer_norm, feed_forward, feed_forward_norm):
+    def __init__(self, mixer, mixer_norm, feed_forward=None, feed_forward_norm=None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer = mixer
         self.mixer_norm = mixer_norm
         self.feed_forward = feed_forward
@@ -37,7 +39,7 @@ class PreNormBlock:
         if not self._asked:
             self._asked = True
             offer = getattr(getattr(self.mixer, "ops", None), "layer_program", None)
-            program = offer() if offer is not None else None
+            program = offer() if offer is not None and self.feed_forward is not None else None
             if program is not None and program.serves(self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm):
                 self._program = program
         return self._program
@@ -54,6 +56,8 @@ class PreNormBlock:
                                       self.feed_forward_norm, resid, delta, ctx, run)
         hidden = self.mixer_norm.add_norm(resid, delta)
         delta = self.mixer.forward(hidden, ctx, run)
+        if self.feed_forward is None:   # a layer of a mixer alone
+            return resid, delta
         hidden = self.feed_forward_norm.add_norm(resid, delta)
         delta = self.feed_forward.forward(hidden, ctx)
         return resid, delta

@@ -43,22 +43,28 @@ class TokenEmbedding:
 class PassEntry:
     """What entering pass t over a run of repeated layers does to the residual: the embedding's output is
     added again (every pass but the first) and the learned vector step[t], in 32-bit, in the kernel that
-    also adds whatever branch outputs are still pending."""
+    also adds whatever branch outputs are still pending.  With `mix`, the residual x is instead replaced
+    by Win [x ; e] + step[t] in every pass, the first included (e: the embedding's output)."""
 
     capture_safe = True
 
     @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
-        return {"step": ParamSpec((spec.passes, spec.width), "bias")}
+        params = {"step": ParamSpec((spec.passes, spec.width), "bias")}
+        if getattr(spec, "mix", False):
+            params["in"] = ParamSpec((spec.width, 2 * spec.width), "mix")
+        return params
 
     def __init__(self, spec, tensors, ops, runtime):
         self.spec, self.ops, self.runtime = spec, ops, runtime
         self.step = tensors["step"].to(torch.float32).contiguous()
+        self.mix = bool(getattr(spec, "mix", False))
+        self.w_in = tensors["in"].contiguous() if self.mix else None
         self._kept = None
 
     def before_embedding(self, ctx) -> None:
         self._kept = None
-        if self.spec.add_embedding and self.spec.passes > 1:
+        if self.mix or (self.spec.add_embedding and self.spec.passes > 1):
             self._kept = self.runtime.buffer("embedding_out", (ctx.num_tokens, self.spec.width), torch.float32)
             ctx.carried["embedding_copy"] = self._kept
 
@@ -70,6 +76,15 @@ class PassEntry:
         if not 0 <= number < self.spec.passes:
             raise ValueError(f"pass {number} of {self.spec.passes}")
         terms = PendingSum.of(delta)
+        if self.mix:
+            # x <- Win [x ; e] + step[t]: the pending sums are added, the residual and the kept embedding are laid
+            # side by side in the engine's type by one kernel, and the product's 32-bit result, which reads
+            # that copy only, overwrites the residual
+            rt = self.runtime
+            both = rt.buffer("pass_both", (resid.shape[0], 2 * self.spec.width), rt.act_dtype)
+            self.ops.concat_cast(resid, terms, self._kept, both)
+            self.ops.linear(both, self.w_in, resid, bias=self.step[number])
+            return resid, None
         if number > 0 and self._kept is not None:
             terms.append((self._kept, 1.0))
         while len(terms) > 4:
@@ -116,6 +131,9 @@ class LMHead:
         logits = self.runtime.buffer("logits", (hidden.shape[0], self.spec.vocab), torch.float32)
         if hidden.shape[0]:
             self.ops.linear(hidden, self.weight, logits)
+            scale = float(getattr(self.spec, "scale", 1.0))
+            if scale != 1.0:
+                logits.mul_(scale)
         return logits
 
 

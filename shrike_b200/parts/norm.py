@@ -25,13 +25,16 @@ class RMSNorm:
 
     @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
-        return {"weight": ParamSpec((spec.width,), "norm")}
+        return {"weight": ParamSpec((spec.width,), "around_zero" if getattr(spec, "offset", 0.0) else "norm")}
 
     def __init__(self, spec, tensors, ops, runtime):
         self.spec = spec
         self.ops = ops
         self.runtime = runtime
         self.weight = tensors["weight"].to(torch.float32).contiguous()
+        offset = float(getattr(spec, "offset", 0.0))
+        if offset:   # a weight stored around zero: the sum is formed once, in 32-bit
+            self.weight = (self.weight + offset).contiguous()
 
     def add_norm(self, resid, delta, out_name="normed"):
         out = self.runtime.buffer(out_name, (resid.shape[0], self.spec.width), self.runtime.act_dtype)

@@ -2,7 +2,8 @@
 
 Azimml/shrike always loads a real snapshot; this mode exists so that tests and
 benchmarks need no network.  Matrices and tables are N(0, 0.02), biases N(0, 0.02),
-norm weights 1 + N(0, 0.1).  Each tensor has its own stream, seeded from the seed
+norm weights 1 + N(0, 0.1)
+(weights kept around zero N(0, 0.1), softmax sinks N(0, 1), a pass entry's matrix the identity plus N(0, 0.02)).  Each tensor has its own stream, seeded from the seed
 and the tensor's name, so a tensor's values do not depend on which others exist.
 
     python -m shrike_b200.weights.random_init --config config.json --seed 0 --out DIR
@@ -34,6 +35,13 @@ def random_tensor(name: str, spec, seed: int, device="cpu", dtype=torch.float32)
     values = torch.randn(spec.shape, generator=generator, device=device, dtype=torch.float32)
     if spec.init == "norm":
         values = 1.0 + 0.1 * values
+    elif spec.init == "around_zero":
+        values = 0.1 * values
+    elif spec.init == "sink":
+        pass
+    elif spec.init == "mix":   # [W, 2 W]: the identity on the first half plus noise, so that a residual stays one
+        values = 0.02 * values
+        values[:, : spec.shape[0]] += torch.eye(spec.shape[0], device=device)
     else:
         values = 0.02 * values
     return values.to(dtype)

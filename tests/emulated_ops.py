@@ -193,6 +193,73 @@ class EmulatedOps:
             flat = latents.view(-1, latents.shape[-2] * latents.shape[-1])
             flat[slots.long()] = wide.to(flat.dtype)
 
+    def concat_cast(self, resid, terms, other, out):
+        for tensor, scale in terms:
+            resid.add_(scale * (tensor.float().sum(0) if tensor.dim() == 3 else tensor.float()))
+        width = resid.shape[1]
+        out[:, :width] = resid.to(out.dtype)
+        out[:, width:] = other.to(out.dtype)
+
+    def decay_scan(self, fused, decays, state, q_start, state_slot, out, num_seqs, num_heads, dim, vdim, longest=0):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        x = fused.float()
+        qk, vw = num_heads * dim, num_heads * vdim
+        act = lambda z: z * torch.sigmoid(z)  # noqa: E731
+        q, k = act(x[:, :qk]).view(-1, num_heads, dim), act(x[:, qk:2 * qk]).view(-1, num_heads, dim)
+        v = act(x[:, 2 * qk:2 * qk + vw]).view(-1, num_heads, vdim)
+        for s in range(num_seqs):
+            slot = int(state_slot[s])
+            if slot < 0:
+                continue
+            held = state[slot][:, : dim * vdim].reshape(num_heads, dim, vdim).clone()
+            for t in range(int(q_start[s]), int(q_start[s + 1])):
+                held = decays.view(-1, 1, 1) * held + k[t, :, :, None] * v[t, :, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", held, q[t]).reshape(-1)
+            state[slot][:, : dim * vdim] = held.reshape(num_heads, -1)
+
+    def norm_gate(self, x, gate_source, gate_at, weight, eps, out):
+        y = x.float()
+        if weight is not None:
+            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight
+        if gate_source is not None:
+            if gate_source.dim() == 3:
+                gate_source = gate_source.sum(0)
+            y = y * torch.sigmoid(gate_source[:, gate_at: gate_at + y.shape[1]].float())
+        out.copy_(y.to(out.dtype))
+
+    def latent_rope_store(self, fused, latent_weight, eps, positions, inv_freq, gain, q_out, latents, slots, heads, rank,
+                          rot, padded):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        n, x = fused.shape[0], fused.float()
+        angle = positions.float()[:, None] * inv_freq[None, :]
+        cos, sin = angle.cos() * gain, angle.sin() * gain
+
+        def turn(t):   # [..., rot], dimension i with i + rot/2
+            a, b = t[..., : rot // 2], t[..., rot // 2:]
+            shape = (n,) + (1,) * (t.dim() - 2) + (rot // 2,)
+            return torch.cat([a * cos.view(shape) - b * sin.view(shape), b * cos.view(shape) + a * sin.view(shape)], -1)
+
+        q = x[:, : heads * (rank + rot)].view(n, heads, rank + rot)
+        wide = torch.zeros(n, heads, padded)
+        wide[..., :rank] = q[..., :rank]
+        wide[..., rank: rank + rot] = turn(q[..., rank:])
+        q_out.copy_(wide.view(n, -1).to(q_out.dtype))
+        if latents is not None:
+            at = heads * (rank + rot)
+            c = x[:, at: at + rank]
+            row = torch.zeros(n, padded)
+            row[:, :rank] = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * latent_weight
+            row[:, rank: rank + rot] = turn(x[:, at + rank: at + rank + rot])
+            flat = latents.view(-1, latents.shape[-2] * latents.shape[-1])
+            keep = slots.long() >= 0
+            flat[slots.long()[keep]] = row[keep].to(flat.dtype)
+
+    def head_linear(self, x, w, out, heads):
+        n = x.shape[0]
+        out.copy_(torch.einsum("nhp,hvp->nhv", x.float().view(n, heads, -1), w.float()).reshape(n, -1).to(out.dtype))
+
     def head_scale(self, x, gate, heads, dim):
         n = x.shape[0]
         x.copy_((x.float().view(n, heads, dim) * gate[:, :, None]).view(n, -1).to(x.dtype))
@@ -259,7 +326,8 @@ class EmulatedOps:
 
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
-                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None):
+                        max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None,
+                        sinks=None):
         page = keys.shape[1]
         group = num_heads // num_kv_heads
         n = q.shape[0]
@@ -282,7 +350,11 @@ class EmulatedOps:
                 scores = softcap * torch.tanh(scores / softcap)
             if slopes is not None:
                 scores = scores - slopes.view(num_kv_heads, group, 1) * (last - idx).float()
-            probs = scores.softmax(-1)
+            if sinks is not None:   # one more term in the denominator, without a key or a value
+                both = torch.cat([scores, sinks.float().view(num_kv_heads, group, 1)], dim=-1)
+                probs = both.softmax(-1)[..., :-1]
+            else:
+                probs = scores.softmax(-1)
             o = torch.einsum("kgc,ckd->kgd", probs, v)
             out[token] = o.reshape(-1).to(out.dtype)
 
