@@ -84,6 +84,18 @@ def turn_pairs(x: torch.Tensor, positions: torch.Tensor, rot: dict) -> torch.Ten
     return out
 
 
+def decayed_recurrence(q, k, v, decay, state=None):
+    """q, k [n, H, D], v [n, H, V], decay [H]: S <- decay S + k v^T token by token from `state` ([H, D, V]; None:
+    zeros), o = S^T q.  Returns (o [n, H, V], the state after the last token)."""
+    n, heads, dim = q.shape
+    state = torch.zeros(heads, dim, v.shape[-1], dtype=q.dtype) if state is None else state.clone()
+    out = torch.zeros(n, heads, v.shape[-1], dtype=q.dtype)
+    for t in range(n):
+        state = decay[:, None, None] * state + k[t, :, :, None] * v[t, :, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+    return out, state
+
+
 def lightning(h, weights, prefix, spec, eps, rounding, states_out=None) -> torch.Tensor:
     n, dtype = h.shape[0], h.dtype
     heads, dim, vdim = spec["heads"], spec["dim"], spec["vdim"]
@@ -91,17 +103,37 @@ def lightning(h, weights, prefix, spec, eps, rounding, states_out=None) -> torch
     q = _r(silu(h @ w("q").T), rounding).view(n, heads, dim)
     k = _r(silu(h @ w("k").T), rounding).view(n, heads, dim)
     v = _r(silu(h @ w("v").T), rounding).view(n, heads, vdim)
-    decay = torch.tensor(spec["decay"], dtype=dtype)
-    state = torch.zeros(heads, dim, vdim, dtype=dtype)
-    out = torch.zeros(n, heads, vdim, dtype=dtype)
-    for t in range(n):
-        state = decay[:, None, None] * state + k[t, :, :, None] * v[t, :, None, :]
-        out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+    out, state = decayed_recurrence(q, k, v, torch.tensor(spec["decay"], dtype=dtype))
     if states_out is not None:
         states_out.append(state)
     flat = unit_rms(out.reshape(n, heads * vdim), eps) * w("norm")
     gated = flat * torch.sigmoid(h @ w("g").T)
     return _r(gated, rounding) @ w("o").T
+
+
+def attend(q, k, v, scale, sinks=None, window=None, first_position=0) -> torch.Tensor:
+    """q [m, H, D] are the queries of positions first_position .. first_position + m - 1, k [ctx, G, D] and
+    v [ctx, G, V] the keys and values of positions 0 .. ctx - 1.  Query head a reads key/value head a // (H / G);
+    position i sees j <= i, with a window only i - window < j.  `sinks` [H]: exp(sink) is one more term of the
+    softmax's denominator.  Returns [m, H, V]."""
+    m, heads, _ = q.shape
+    share = heads // k.shape[1]
+    at = first_position + torch.arange(m)
+    distance = at[:, None] - torch.arange(k.shape[0])[None, :]
+    seen = distance >= 0
+    if window is not None:
+        seen = seen & (distance < window)
+    out = torch.zeros(m, heads, v.shape[-1], dtype=q.dtype)
+    for a in range(heads):
+        scores = ((q[:, a] @ k[:, a // share].T) * scale).masked_fill(~seen, -math.inf)
+        if sinks is None:
+            weight = torch.softmax(scores, dim=-1)
+        else:
+            top = torch.maximum(scores.max(-1, keepdim=True).values, sinks[a])
+            weight = torch.exp(scores - top)
+            weight = weight / (weight.sum(-1, keepdim=True) + torch.exp(sinks[a] - top))
+        out[:, a] = weight @ v[:, a // share]
+    return out
 
 
 def sink_attention(h, weights, prefix, spec, rounding) -> torch.Tensor:
@@ -113,17 +145,7 @@ def sink_attention(h, weights, prefix, spec, rounding) -> torch.Tensor:
     k = _r(h @ w("k").T + w("k.b"), rounding).view(n, groups, dim)
     v = _r(h @ w("v").T + w("v.b"), rounding).view(n, groups, vdim)
     q, k = _r(turn_pairs(q, positions, spec["rot"]), rounding), _r(turn_pairs(k, positions, spec["rot"]), rounding)
-    share = heads // groups
-    out = torch.zeros(n, heads, vdim, dtype=dtype)
-    causal = positions[None, :] <= positions[:, None]
-    for a in range(heads):
-        scores = (q[:, a] @ k[:, a // share].T) * spec["scale"]
-        scores = scores.masked_fill(~causal, -math.inf)
-        sink = w("sink")[a]
-        top = torch.maximum(scores.max(-1, keepdim=True).values, sink)
-        weight = torch.exp(scores - top)
-        weight = weight / (weight.sum(-1, keepdim=True) + torch.exp(sink - top))
-        out[:, a] = weight @ v[:, a // share]
+    out = attend(q, k, v, spec["scale"], sinks=w("sink"))
     return _r(out.reshape(n, heads * vdim), rounding) @ w("o").T
 
 
@@ -139,12 +161,11 @@ def latent_attention(h, weights, prefix, spec, eps, rounding) -> torch.Tensor:
     q_turned = _r(turn_pairs(q[..., dim:], positions, spec["rot"]), rounding)
     keys = _r(latent @ w("uk").T, rounding).view(n, heads, dim)
     values = _r(latent @ w("uv").T, rounding).view(n, heads, vdim)
-    distance = positions[:, None] - positions[None, :]
-    seen = (distance >= 0) & (distance < spec["mask"]["size"])
-    out = torch.zeros(n, heads, vdim, dtype=dtype)
-    for a in range(heads):
-        scores = (q[:, a, :dim] @ keys[:, a].T + q_turned[:, a] @ shared.T) * spec["scale"]
-        out[:, a] = torch.softmax(scores.masked_fill(~seen, -math.inf), dim=-1) @ values[:, a]
+    # per head the key is [Wuk c | the shared turned part]
+    full_q = torch.cat([q[..., :dim], q_turned], dim=-1)
+    full_k = torch.cat([keys, shared[:, None, :].expand(n, heads, turned)], dim=-1)
+    window = spec["mask"]["size"] if spec.get("mask") is not None else None   # the latest keys, the query's own included
+    out = attend(full_q, full_k, values, spec["scale"], window=window)
     gated = out.reshape(n, heads * vdim) * torch.sigmoid(h @ w("g").T)
     return _r(gated, rounding) @ w("o").T
 
