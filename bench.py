@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -476,7 +477,7 @@ def run_mixed(args) -> dict:
 
     torch.cuda.set_device(0)
     design = getattr(args, "arch", "qwen2")   # the same workload on another decoder at the same widths
-    sadodra = design in ("sadodra", "vupitar")
+    sadodra = design in ("sadodra", "vupitar", "kavedra")
     if sadodra:
         from shrike_b200.shapes import shape_config
 
@@ -611,6 +612,53 @@ def run_case(args) -> dict:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
         work = {"bytes": tokens * (total * 4 + (heads + 2 * kv) * d * 2 + heads * 4)}
+    elif args.case in ("decay_scan", "decay_scan_single"):
+        # linear attention with a decay per head at the 7B-width shape (28 heads of 128 x 128): one prompt of
+        # --prefill-tokens tokens (runs of 64 tokens), or --batch sequences one token each (the walk)
+        lh, ld, lv = heads, d, d
+        single = args.case.endswith("_single")
+        seqs, q_len = (tokens, 1) if single else (1, args.prefill_tokens)
+        n = seqs * q_len
+        total = -(-(2 * lh * ld + 2 * lh * lv) // 16) * 16
+        fused = torch.randn(n, total, device=dev, dtype=torch.float32) * 0.3
+        decays = torch.tensor([math.exp(-1.0 / (8.0 * 2.0 ** (7.0 * i / (lh - 1)))) for i in range(lh)], device=dev)
+        state = torch.zeros(seqs, lh, ld * lv, device=dev)
+        q_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        out = torch.empty(n, lh * lv, device=dev)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.decay_scan(fused, decays, state, q_start, slots, out, seqs, lh, ld, lv, longest=q_len)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        chunks = -(-q_len // 64)
+        # per head and run of 64 tokens: scores 64 x 64 x dim, their outputs 64 x 64 x vdim, the state's addition and the
+        # state's part of the outputs 2 x 64 x dim x vdim (2 flops a multiply-add)
+        work = {"bytes": seqs * lh * ld * lv * 4 * 2 + n * (2 * lh * ld + lh * lv) * 4 + n * lh * lv * 4} if single else \
+               {"flops": 2.0 * seqs * lh * chunks * (64 * 64 * ld + 64 * 64 * lv + 2 * 64 * ld * lv)}
+    elif args.case == "latent_rope_store":
+        # queries, latent and shared key part of the 7B-width latent attention (28 heads, rank 192 + 64 rotated) from the
+        # fused product's float32 result: the latent's norm, the rotation, casts, page rows (--batch tokens)
+        rank, rot = 192, 64
+        padded = rank + rot
+        total = -(-(heads * padded + padded) // 16) * 16
+        fused = torch.randn(tokens, total, device=dev, dtype=torch.float32)
+        positions = torch.arange(tokens, dtype=torch.int32, device=dev)
+        inv_freq = torch.tensor([1e4 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
+        weight = torch.ones(rank, device=dev)
+        q = torch.empty(tokens, heads * padded, device=dev, dtype=torch.bfloat16)
+        pages = -(-tokens // BLOCK_SIZE)
+        latents = torch.empty(pages, BLOCK_SIZE, 1, padded, device=dev, dtype=torch.bfloat16)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.latent_rope_store(fused, weight, 1e-6, positions, inv_freq, 1.0, q, latents, positions, heads, rank, rot, padded)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": tokens * (total * 4 + (heads + 1) * padded * 2)}
     elif args.case in ("matrix_memory", "matrix_memory_single"):
         # the matrix memory of the 7B-width shape (8 heads of 128 x 256): one prompt of --prefill-tokens tokens (chunk
         # kernels), or --batch sequences one token each (the walk)
@@ -641,13 +689,14 @@ def run_case(args) -> dict:
         work = {"bytes": seqs * mh * (md * mv + md) * 4 * 2 + n * total * 4} if single else \
                {"flops": 2.0 * seqs * mh * chunks * (64 * 64 * md + 64 * 64 * mv + 2 * 64 * md * mv)}
     elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores",
-                       "attention_single_latent", "attention_portions_latent"):
+                       "attention_single_latent", "attention_portions_latent", "attention_single_sink", "attention_portions_sink"):
         single = args.case.startswith("attention_single")
         if args.case.endswith("_latent"):   # one key/value head of 256 whose keys are its values, as a cached latent is read
             kv, d = 1, 256
         changed = args.case.endswith("_scores")   # a soft cap and a distance bias on every score
         softcap = 50.0 if changed else None
         slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / heads) for i in range(heads)], device=dev) if changed else None
+        sinks = torch.linspace(-1.0, 1.0, heads, device=dev) if args.case.endswith("_sink") else None   # one more term of every denominator
         seqs = tokens if single else 1
         ctx_len = CONTEXT if single else args.prefill_tokens
         q_len = 1 if single else args.prefill_tokens
@@ -667,7 +716,7 @@ def run_case(args) -> dict:
             keep_busy()
             start.record()
             ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, None, out,
-                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs, softcap=softcap, slopes=slopes)
+                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs, softcap=softcap, slopes=slopes, sinks=sinks)
             stop.record()
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) * 1e3)
@@ -779,7 +828,7 @@ def run_timeline(args) -> dict:
 
 
 def run_design(args) -> dict:
-    """A design (--arch sadodra, the default here, or vupitar) beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
+    """A design (--arch sadodra, the default here, vupitar or kavedra) beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
     closest model this engine serves), random weights: one 2,048-token prompt in one step, and decoding
     at --batch sequences of --context tokens, device-timed through the step function and the sampling
     kernel; for each, the kernels of one step by the time they take (CUPTI activity records).
@@ -944,7 +993,7 @@ def main():
     parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
-    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra", "vupitar"],
+    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra", "vupitar", "kavedra"],
                         help="--workload mixed: the decoder the 64 requests run on (all at Qwen2.5-1.5B widths); "
                              "--case design: the design that is set beside the Qwen2 decoder (default there: sadodra)")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
@@ -956,8 +1005,9 @@ def main():
     parser.add_argument("--case", default=None,
                         help="run a small single-kernel workload instead (for profiling): gemm_gate_up, gemm_down, "
                              "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased; with _latent: "
-                             "one key/value head of 256 whose keys are its values), "
-                             "branch_norm, tanh_norm, head_prep, matrix_memory (a prompt of --prefill-tokens), matrix_memory_single; "
+                             "one key/value head of 256 whose keys are its values; with _sink: a sink in every softmax), "
+                             "branch_norm, tanh_norm, head_prep, matrix_memory (a prompt of --prefill-tokens), matrix_memory_single, "
+                             "decay_scan (a prompt of --prefill-tokens), decay_scan_single, latent_rope_store; "
                              "--batch gives tokens / sequences / rows.  timeline: per-kernel "
                              "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
                              "beside the Qwen2 decoder of equal widths (--design), prefill and decode")

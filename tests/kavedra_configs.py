@@ -146,3 +146,62 @@ def make_kavedra_folder(tmp_path, key: str, dtype: str = "float32", raw: dict | 
     (out / "config.json").write_text(json.dumps(raw, indent=2) + "\n")
     write_safetensors(out / "model.safetensors", tensors, {"format": "pt", "seed": str(seed)})
     return out
+
+
+MARK, ASKER = 3, 4   # token ids of `planted_pair`
+
+
+def planted_pair(raw: dict, strength: float = 2.0, gain: float = 12.0):
+    """A `change` for `make_kavedra_folder` on a model whose layer 0 is an attention or a latent attention: the
+    score between a query of token ASKER and a key of token MARK stands far above every other score, in every
+    head, so that whether MARK is seen from ASKER's position decides ASKER's logits however many keys lie between.
+    On a linear attention the same pair makes MARK's value stand out in what ASKER reads from the state.
+
+    Residual axis 0 is nonzero in MARK's embedding only and axis 1 in ASKER's only; one unrotated key dimension
+    reads axis 0 alone and the same query dimension reads axis 1 alone.  The output projection is made larger so that
+    what the heads attend to is a good part of the residual."""
+    layer = raw["layers"][0]
+    spec = layer["mixer"]
+
+    def change(tensors):
+        embed = tensors["embed"]
+        embed[:, 0:2] = 0.0
+        embed[MARK, 0] = strength
+        embed[ASKER, 1] = strength
+        tensors["l0.norm1"][0:2] = 0.0
+        tensors["l0.mix.o"] *= 4.0
+        heads, dim = spec["heads"], spec["dim"]
+        if layer["type"] == "latent_attention":
+            per_head = dim + spec["rot_dim"]
+            tensors["l0.mix.dkv"][0] = 0.0
+            tensors["l0.mix.dkv"][0, 0] = gain       # latent component 0 is MARK's alone
+            tensors["l0.mix.dkv.norm"][0] = 1.0
+            for a in range(heads):
+                tensors["l0.mix.uk"][a * dim] = 0.0
+                tensors["l0.mix.uk"][a * dim, 0] = 4.0
+                tensors["l0.mix.q"][a * per_head] = 0.0
+                tensors["l0.mix.q"][a * per_head, 1] = gain
+        elif layer["type"] == "attention":
+            at = dim - 1                             # the head's last dimension
+            if spec["rot"]["dims"] > at:
+                raise ValueError("the planted dimension must lie outside the rotated ones")
+            for g in range(spec["kv_heads"]):
+                tensors["l0.mix.k"][g * dim + at] = 0.0
+                tensors["l0.mix.k"][g * dim + at, 0] = gain
+                tensors["l0.mix.k.b"][g * dim + at] = 0.0
+            for a in range(heads):
+                tensors["l0.mix.q"][a * dim + at] = 0.0
+                tensors["l0.mix.q"][a * dim + at, 1] = gain
+                tensors["l0.mix.q.b"][a * dim + at] = 0.0
+        elif layer["type"] == "lightning":
+            # key dimension 0 of every head is large for MARK alone, query dimension 0 for ASKER alone: what ASKER reads
+            # from the state's row 0 is MARK's value, times the head's decay to the power of the distance
+            for a in range(heads):
+                tensors["l0.mix.k"][a * dim] = 0.0
+                tensors["l0.mix.k"][a * dim, 0] = gain
+                tensors["l0.mix.q"][a * dim] = 0.0
+                tensors["l0.mix.q"][a * dim, 1] = gain
+        else:
+            raise ValueError(layer["type"])
+
+    return change
