@@ -126,6 +126,7 @@ struct ChunkArgs {
   float* chunk_state;       // [runs][heads][dim * vdim]: L_c, then S_before(c)
   int num_seqs;
   int skip;                 // sequences of at most this many new tokens have no runs (they walk)
+  int span;                 // value columns one CTA of `local` and `finish` serves, a multiple of MAX_SLICE
 };
 
 // Run number `run` of the batch: its sequence, first token and token count.  False: there is no such run.
@@ -146,68 +147,169 @@ __device__ __forceinline__ bool locate_run(const ChunkArgs& c, int run, int& seq
   return false;
 }
 
-// grid (vdim slices, heads, chunks): intra-run outputs and L_c for a slice of columns.
+// The three products of a run (scores, scores times values, keys times values) and the product of `finish` run as
+// register tiles over shared memory: 256 threads as 16 x 16, thread (ty, tx) owning rows ty + 16 r and either rows
+// tx + 16 c of the other operand (scores) or columns 4 tx .. 4 tx + 3 (the others), four reduction steps a 16-byte load.
+// Rows of q and k are padded to `chunk_pitch` floats, a multiple of four whose quarter is odd: the sixteen rows a
+// half-warp reads at once fall into different banks.
+__host__ __device__ __forceinline__ int chunk_pitch(int dim) { return ((dim + 7) & ~7) + 4; }
+constexpr int SCORE_PITCH = CHUNK + 4;
+
+__device__ __forceinline__ void fma4(float (&acc)[4], float w, const float4& v) {
+  acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]); acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+}
+
+// silu of columns [at, at + width) of the fused projection for tokens first .. first + count - 1 into dst[j * pitch + e];
+// rows from `count` on and columns from `width` to `fill_to` are zero
+__device__ __forceinline__ void stage_rows(float* dst, int pitch, int fill_to, const ScanArgs& a, int first, int count, int at,
+                                           int width) {
+  const bool wide = a.partials == 1 && (width & 3) == 0 && (fill_to & 3) == 0 && (at & 3) == 0 && (a.row_width & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(a.fused) & 15) == 0;
+  if (wide) {
+    const int quads = fill_to >> 2;
+    for (int i = threadIdx.x; i < CHUNK * quads; i += THREADS) {
+      const int j = i / quads, e = (i - j * quads) << 2;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < count && e < width) {
+        v = *reinterpret_cast<const float4*>(a.fused + static_cast<size_t>(first + j) * a.row_width + at + e);
+        v.x = silu(v.x); v.y = silu(v.y); v.z = silu(v.z); v.w = silu(v.w);
+      }
+      *reinterpret_cast<float4*>(dst + j * pitch + e) = v;
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < CHUNK * fill_to; i += THREADS) {
+    const int j = i / fill_to, e = i - j * fill_to;
+    float v = 0.f;
+    if (j < count && e < width)
+      v = silu(sum_partials(a.fused + static_cast<size_t>(first + j) * a.row_width + at + e, a.partial_stride, a.partials));
+    dst[j * pitch + e] = v;
+  }
+}
+
+// grid (column groups of `span`, heads, runs): intra-run outputs and L_c, 64 columns at a time.
 __global__ void __launch_bounds__(THREADS) chunk_local_kernel(ChunkArgs c) {
   extern __shared__ __align__(16) float shared[];
   const ScanArgs& a = c.s;
-  float* q_s = shared;                              // [CHUNK][dim + 1]
-  float* k_s = q_s + CHUNK * (a.dim + 1);           // [CHUNK][dim + 1]
-  float* v_s = k_s + CHUNK * (a.dim + 1);           // [CHUNK][slice]
-  float* w_s = v_s + CHUNK * a.slice;               // [CHUNK][CHUNK + 1] decayed scores
+  const int pitch = chunk_pitch(a.dim), dim8 = (a.dim + 7) & ~7, dim4 = (a.dim + 3) & ~3;
+  float* q_s = shared;                              // [CHUNK][pitch]
+  float* k_s = q_s + CHUNK * pitch;                 // [CHUNK][pitch]
+  float* v_s = k_s + CHUNK * pitch;                 // [CHUNK][MAX_SLICE]
+  float* w_s = v_s + CHUNK * MAX_SLICE;             // [CHUNK][SCORE_PITCH] decayed scores, zero above the diagonal
+  float* pow_s = w_s + CHUNK * SCORE_PITCH;         // [CHUNK + 1] d^n
   let_dependents_start();
   wait_for_previous();
-  const int run = blockIdx.z, head = blockIdx.y, first_col = blockIdx.x * a.slice;
+  const int run = blockIdx.z, head = blockIdx.y;
   int seq, first, count;
   if (!locate_run(c, run, seq, first, count)) return;
   const int slot = a.state_slot[seq];
   if (slot < 0 || slot >= a.num_slots) return;
-  const int cols = min(a.slice, a.vdim - first_col);
-  const int t = threadIdx.x, pitch = a.dim + 1;
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
   const float d = a.decays[head];
-  const int q_at = head * a.dim, k_at = a.heads * a.dim + head * a.dim, v_at = 2 * a.heads * a.dim + head * a.vdim + first_col;
-  for (int i = t; i < count * a.dim; i += THREADS) {
-    const int j = i / a.dim, e = i - j * a.dim;
-    const float* row = a.fused + static_cast<size_t>(first + j) * a.row_width;
-    q_s[j * pitch + e] = silu(sum_partials(row + q_at + e, a.partial_stride, a.partials));
-    k_s[j * pitch + e] = silu(sum_partials(row + k_at + e, a.partial_stride, a.partials));
-  }
-  for (int i = t; i < count * cols; i += THREADS) {
-    const int j = i / cols, e = i - j * cols;
-    const float* row = a.fused + static_cast<size_t>(first + j) * a.row_width;
-    v_s[j * a.slice + e] = silu(sum_partials(row + v_at + e, a.partial_stride, a.partials));
-  }
+  const int q_at = head * a.dim, k_at = a.heads * a.dim + head * a.dim;
+  stage_rows(q_s, pitch, dim8, a, first, count, q_at, a.dim);
+  stage_rows(k_s, pitch, dim8, a, first, count, k_at, a.dim);
+  for (int n = t; n <= CHUNK; n += THREADS) pow_s[n] = int_power(d, n);
   __syncthreads();
-  // decayed scores w[i][j] = d^(i - j) q_i . k_j for j <= i
-  for (int i = t; i < count * count; i += THREADS) {
-    const int qi = i / count, kj = i - qi * count;
-    float dot = 0.f;
-    if (kj <= qi) {
-      for (int e = 0; e < a.dim; ++e) dot = fmaf(q_s[qi * pitch + e], k_s[kj * pitch + e], dot);
-      dot *= int_power(d, qi - kj);
+  {   // decayed scores w[i][j] = d^(i - j) q_i . k_j for j <= i: rows ty + 16 r, keys tx + 16 c, only c <= r can be seen
+    float acc[4][4] = {};
+    for (int e = 0; e < dim4; e += 4) {
+      float4 qv[4], kv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) qv[r] = *reinterpret_cast<const float4*>(q_s + (ty + 16 * r) * pitch + e);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) kv[r] = *reinterpret_cast<const float4*>(k_s + (tx + 16 * r) * pitch + e);
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int cc = 0; cc <= r; ++cc) {
+          acc[r][cc] = fmaf(qv[r].x, kv[cc].x, acc[r][cc]);
+          acc[r][cc] = fmaf(qv[r].y, kv[cc].y, acc[r][cc]);
+          acc[r][cc] = fmaf(qv[r].z, kv[cc].z, acc[r][cc]);
+          acc[r][cc] = fmaf(qv[r].w, kv[cc].w, acc[r][cc]);
+        }
     }
-    w_s[qi * (CHUNK + 1) + kj] = dot;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const int qi = ty + 16 * r, kj = tx + 16 * cc;
+        w_s[qi * SCORE_PITCH + kj] = (cc <= r && kj <= qi && qi < count) ? acc[r][cc] * pow_s[qi - kj] : 0.f;
+      }
   }
-  __syncthreads();
-  for (int i = t; i < count * cols; i += THREADS) {
-    const int qi = i / cols, e = i - qi * cols;
-    float sum = 0.f;
-    for (int kj = 0; kj <= qi; ++kj) sum = fmaf(w_s[qi * (CHUNK + 1) + kj], v_s[kj * a.slice + e], sum);
-    a.out[static_cast<size_t>(first + qi) * a.heads * a.vdim + head * a.vdim + first_col + e] = sum;
-  }
-  // L_c[r][e] = sum_j d^(count - 1 - j) k_j[r] v_j[e]; the powers go into w_s's first row
-  __syncthreads();
-  for (int j = t; j < count; j += THREADS) w_s[j] = int_power(d, count - 1 - j);
-  __syncthreads();
+  const int v_first = 2 * a.heads * a.dim + head * a.vdim;
+  const size_t out_pitch = static_cast<size_t>(a.heads) * a.vdim;
+  const bool wide_out = (a.vdim & 3) == 0;
   float* local = c.chunk_state + (static_cast<size_t>(run) * a.heads + head) * a.dim * a.vdim;
-  for (int i = t; i < a.dim * cols; i += THREADS) {
-    const int r = i / cols, e = i - r * cols;
-    float sum = 0.f;
-    for (int j = 0; j < count; ++j) sum = fmaf(w_s[j] * k_s[j * pitch + r], v_s[j * a.slice + e], sum);
-    local[static_cast<size_t>(r) * a.vdim + first_col + e] = sum;
+  const int last_col = min(a.vdim, (static_cast<int>(blockIdx.x) + 1) * c.span);
+  for (int first_col = blockIdx.x * c.span; first_col < last_col; first_col += MAX_SLICE) {
+    const int cols = min(MAX_SLICE, a.vdim - first_col);
+    __syncthreads();   // the scores are whole; the pass before is done with v_s
+    stage_rows(v_s, MAX_SLICE, MAX_SLICE, a, first, count, v_first + first_col, cols);
+    __syncthreads();
+    {   // o_i = sum_(j <= i) w[i][j] v_j: rows ty + 16 r, columns 4 tx .., keys sixteen at a time (block jb reaches rows r >= jb)
+      float o[4][4] = {};
+#pragma unroll
+      for (int jb = 0; jb < 4; ++jb) {
+        if (16 * jb >= count) break;
+#pragma unroll
+        for (int j = 16 * jb; j < 16 * jb + 16; j += 4) {
+          float4 vv[4];
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) vv[kk] = *reinterpret_cast<const float4*>(v_s + (j + kk) * MAX_SLICE + 4 * tx);
+#pragma unroll
+          for (int r = jb; r < 4; ++r) {
+            const float4 w = *reinterpret_cast<const float4*>(w_s + (ty + 16 * r) * SCORE_PITCH + j);
+            fma4(o[r], w.x, vv[0]); fma4(o[r], w.y, vv[1]); fma4(o[r], w.z, vv[2]); fma4(o[r], w.w, vv[3]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int qi = ty + 16 * r;
+        if (qi >= count) continue;
+        float* dst = a.out + static_cast<size_t>(first + qi) * out_pitch + head * a.vdim + first_col + 4 * tx;
+        if (wide_out) {
+          if (4 * tx < cols) *reinterpret_cast<float4*>(dst) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * tx + e < cols) dst[e] = o[r][e];
+        }
+      }
+    }
+    // L_c[r][e] = sum_j d^(count - 1 - j) k_j[r] v_j[e]: rows 8 ty .. 8 ty + 7 of 128 at a time, columns 4 tx ..
+    for (int base = 0; base < a.dim; base += 128) {
+      const int r0 = base + 8 * ty;
+      if (r0 >= a.dim) continue;
+      float l[8][4] = {};
+      for (int j = 0; j < count; ++j) {
+        float4 v = *reinterpret_cast<const float4*>(v_s + j * MAX_SLICE + 4 * tx);
+        const float p = pow_s[count - 1 - j];
+        v.x *= p; v.y *= p; v.z *= p; v.w *= p;
+        const float4 k0 = *reinterpret_cast<const float4*>(k_s + j * pitch + r0);
+        const float4 k1 = *reinterpret_cast<const float4*>(k_s + j * pitch + r0 + 4);
+        fma4(l[0], k0.x, v); fma4(l[1], k0.y, v); fma4(l[2], k0.z, v); fma4(l[3], k0.w, v);
+        fma4(l[4], k1.x, v); fma4(l[5], k1.y, v); fma4(l[6], k1.z, v); fma4(l[7], k1.w, v);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (r0 + i >= a.dim) continue;
+        float* dst = local + static_cast<size_t>(r0 + i) * a.vdim + first_col + 4 * tx;
+        if (wide_out) {
+          if (4 * tx < cols) *reinterpret_cast<float4*>(dst) = make_float4(l[i][0], l[i][1], l[i][2], l[i][3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * tx + e < cols) dst[e] = l[i][e];
+        }
+      }
+    }
   }
 }
 
-// grid (blocks over dim * vdim, heads, seqs): walks a sequence's runs in order, element by element.
+// grid (blocks over dim * vdim, heads, seqs): walks a sequence's runs in order, element by element; the additions of
+// four runs are asked for together, so that a sequence costs a memory latency every four runs, not every run.
 __global__ void __launch_bounds__(THREADS) chunk_carry_kernel(ChunkArgs c) {
   const ScanArgs& a = c.s;
   let_dependents_start();
@@ -225,51 +327,96 @@ __global__ void __launch_bounds__(THREADS) chunk_carry_kernel(ChunkArgs c) {
     if (other > c.skip) run += (other + CHUNK - 1) / CHUNK;
   }
   const float d = a.decays[head];
+  const float whole = int_power(d, CHUNK);
   float* mine = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.state_stride + element;
+  const size_t per_run = static_cast<size_t>(a.heads) * a.dim * a.vdim;
+  float* local = c.chunk_state + (static_cast<size_t>(run) * a.heads + head) * a.dim * a.vdim + element;
+  const int runs = (length + CHUNK - 1) / CHUNK;
   float held = *mine;
-  for (int done = 0; done < length; done += CHUNK, ++run) {
-    float* local = c.chunk_state + (static_cast<size_t>(run) * a.heads + head) * a.dim * a.vdim + element;
-    const float add = *local;
-    *local = held;                                   // S before this run: what `finish` reads
-    held = fmaf(int_power(d, min(CHUNK, length - done)), held, add);
+  for (int r = 0; r < runs; r += 4) {
+    float add[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) add[i] = r + i < runs ? local[(r + i) * per_run] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (r + i < runs) {
+        local[(r + i) * per_run] = held;             // S before this run: what `finish` reads
+        const int tokens = min(CHUNK, length - (r + i) * CHUNK);
+        held = fmaf(tokens == CHUNK ? whole : int_power(d, tokens), held, add[i]);
+      }
   }
   *mine = held;
 }
 
-// grid (vdim slices, heads, chunks): o_t += d^(t - a + 1) S_before^T q_t.
+// grid (column groups of `span`, heads, runs): o_t += d^(t - a + 1) S_before^T q_t, 64 columns at a time.
 __global__ void __launch_bounds__(THREADS) chunk_finish_kernel(ChunkArgs c) {
   extern __shared__ __align__(16) float shared[];
   const ScanArgs& a = c.s;
-  float* q_s = shared;                        // [CHUNK][dim + 1]
-  float* s_s = q_s + CHUNK * (a.dim + 1);     // [dim][slice]
+  const int pitch = chunk_pitch(a.dim), dim4 = (a.dim + 3) & ~3;
+  float* q_s = shared;                        // [CHUNK][pitch]
+  float* s_s = q_s + CHUNK * pitch;           // [dim4][MAX_SLICE]
+  float* pow_s = s_s + dim4 * MAX_SLICE;      // [CHUNK + 1]
   let_dependents_start();
   wait_for_previous();
-  const int run = blockIdx.z, head = blockIdx.y, first_col = blockIdx.x * a.slice;
+  const int run = blockIdx.z, head = blockIdx.y;
   int seq, first, count;
   if (!locate_run(c, run, seq, first, count)) return;
   const int slot = a.state_slot[seq];
   if (slot < 0 || slot >= a.num_slots) return;
-  const int cols = min(a.slice, a.vdim - first_col);
-  const int t = threadIdx.x, pitch = a.dim + 1;
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
   const float d = a.decays[head];
-  const int q_at = head * a.dim;
-  for (int i = t; i < count * a.dim; i += THREADS) {
-    const int j = i / a.dim, e = i - j * a.dim;
-    const float* row = a.fused + static_cast<size_t>(first + j) * a.row_width;
-    q_s[j * pitch + e] = silu(sum_partials(row + q_at + e, a.partial_stride, a.partials));
-  }
+  stage_rows(q_s, pitch, (a.dim + 7) & ~7, a, first, count, head * a.dim, a.dim);
+  for (int n = t; n <= CHUNK; n += THREADS) pow_s[n] = int_power(d, n);
   const float* before = c.chunk_state + (static_cast<size_t>(run) * a.heads + head) * a.dim * a.vdim;
-  for (int i = t; i < a.dim * cols; i += THREADS) {
-    const int r = i / cols, e = i - r * cols;
-    s_s[r * a.slice + e] = before[static_cast<size_t>(r) * a.vdim + first_col + e];
-  }
-  __syncthreads();
-  for (int i = t; i < count * cols; i += THREADS) {
-    const int qi = i / cols, e = i - qi * cols;
-    float sum = 0.f;
-    for (int r = 0; r < a.dim; ++r) sum = fmaf(q_s[qi * pitch + r], s_s[r * a.slice + e], sum);
-    float* o = a.out + static_cast<size_t>(first + qi) * a.heads * a.vdim + head * a.vdim + first_col + e;
-    *o = fmaf(int_power(d, qi + 1), sum, *o);
+  const size_t out_pitch = static_cast<size_t>(a.heads) * a.vdim;
+  const bool wide = (a.vdim & 3) == 0;
+  const int last_col = min(a.vdim, (static_cast<int>(blockIdx.x) + 1) * c.span);
+  for (int first_col = blockIdx.x * c.span; first_col < last_col; first_col += MAX_SLICE) {
+    const int cols = min(MAX_SLICE, a.vdim - first_col);
+    __syncthreads();
+    if (wide) {
+      for (int i = t; i < dim4 * (MAX_SLICE / 4); i += THREADS) {
+        const int r = i / (MAX_SLICE / 4), e = (i - r * (MAX_SLICE / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < a.dim && e < cols) v = *reinterpret_cast<const float4*>(before + static_cast<size_t>(r) * a.vdim + first_col + e);
+        *reinterpret_cast<float4*>(s_s + r * MAX_SLICE + e) = v;
+      }
+    } else {
+      for (int i = t; i < dim4 * MAX_SLICE; i += THREADS) {
+        const int r = i / MAX_SLICE, e = i - r * MAX_SLICE;
+        s_s[i] = (r < a.dim && e < cols) ? before[static_cast<size_t>(r) * a.vdim + first_col + e] : 0.f;
+      }
+    }
+    __syncthreads();
+    float acc[4][4] = {};
+    for (int e = 0; e < dim4; e += 4) {
+      float4 sv[4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) sv[kk] = *reinterpret_cast<const float4*>(s_s + (e + kk) * MAX_SLICE + 4 * tx);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 q = *reinterpret_cast<const float4*>(q_s + (ty + 16 * r) * pitch + e);
+        fma4(acc[r], q.x, sv[0]); fma4(acc[r], q.y, sv[1]); fma4(acc[r], q.z, sv[2]); fma4(acc[r], q.w, sv[3]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int qi = ty + 16 * r;
+      if (qi >= count) continue;
+      const float p = pow_s[qi + 1];
+      float* o = a.out + static_cast<size_t>(first + qi) * out_pitch + head * a.vdim + first_col + 4 * tx;
+      if (wide) {
+        if (4 * tx < cols) {
+          float4 v = *reinterpret_cast<float4*>(o);
+          v.x = fmaf(p, acc[r][0], v.x); v.y = fmaf(p, acc[r][1], v.y); v.z = fmaf(p, acc[r][2], v.z); v.w = fmaf(p, acc[r][3], v.w);
+          *reinterpret_cast<float4*>(o) = v;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (4 * tx + e < cols) o[e] = fmaf(p, acc[r][e], o[e]);
+      }
+    }
   }
 }
 
@@ -433,9 +580,9 @@ SHRIKE_API int shrike_decay_scan(const float* fused, int partials, long long par
   if (chunked) {
     ChunkArgs c;
     c.s = a; c.chunk_state = chunk_state; c.num_seqs = num_seqs; c.skip = skip;
-    const size_t pitch = dim + 1;
-    const size_t local_smem = (2 * CHUNK * pitch + static_cast<size_t>(CHUNK) * a.slice + CHUNK * (CHUNK + 1)) * sizeof(float);
-    const size_t finish_smem = (CHUNK * pitch + static_cast<size_t>(dim) * a.slice) * sizeof(float);
+    const size_t pitch = chunk_pitch(dim), dim4 = (static_cast<size_t>(dim) + 3) & ~static_cast<size_t>(3);
+    const size_t local_smem = (2 * CHUNK * pitch + static_cast<size_t>(CHUNK) * MAX_SLICE + CHUNK * SCORE_PITCH + CHUNK + 4) * sizeof(float);
+    const size_t finish_smem = (CHUNK * pitch + dim4 * MAX_SLICE + CHUNK + 4) * sizeof(float);
     const size_t limit = shrike_device().max_smem;
     if (local_smem > limit || finish_smem > limit) return SHRIKE_BAD_ARGUMENT;
     static size_t raised_local = 0, raised_finish = 0;
@@ -449,7 +596,10 @@ SHRIKE_API int shrike_decay_scan(const float* fused, int partials, long long par
         return SHRIKE_BAD_ARGUMENT;
       raised_finish = limit;
     }
-    const dim3 per_chunk(slices, heads, chunks);
+    // a CTA takes every value column of its run and head (q, k and the scores are staged once) when the runs and heads
+    // alone fill the device twice over, else 64 columns
+    c.span = static_cast<long long>(chunks) * heads >= 2ll * shrike_device().sm_count ? slices * MAX_SLICE : MAX_SLICE;
+    const dim3 per_chunk((vdim + c.span - 1) / c.span, heads, chunks);
     err = launch_dependent(chunk_local_kernel, per_chunk, dim3(THREADS), local_smem, stream, c);
     if (err != cudaSuccess) return static_cast<int>(err);
     const dim3 per_seq((dim * vdim + THREADS - 1) / THREADS, heads, num_seqs);
