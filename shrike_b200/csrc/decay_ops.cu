@@ -308,8 +308,11 @@ __global__ void __launch_bounds__(THREADS) chunk_local_kernel(ChunkArgs c) {
   }
 }
 
-// grid (blocks over dim * vdim, heads, seqs): walks a sequence's runs in order, element by element; the additions of
-// four runs are asked for together, so that a sequence costs a memory latency every four runs, not every run.
+// grid (blocks over dim * vdim / VEC, heads, seqs): walks a sequence's runs in order, VEC elements a thread; the
+// additions of eight runs are asked for together, so that a sequence costs a memory latency every eight runs.
+constexpr int CARRY_AHEAD = 8;
+
+template <int VEC>
 __global__ void __launch_bounds__(THREADS) chunk_carry_kernel(ChunkArgs c) {
   const ScanArgs& a = c.s;
   let_dependents_start();
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(THREADS) chunk_carry_kernel(ChunkArgs c) {
   if (slot < 0 || slot >= a.num_slots) return;
   const int length = a.q_start[seq + 1] - a.q_start[seq];
   if (length <= c.skip) return;   // the walk serves it
-  const int element = blockIdx.x * THREADS + threadIdx.x;
+  const int element = (blockIdx.x * THREADS + threadIdx.x) * VEC;
   if (element >= a.dim * a.vdim) return;
   int run = 0;   // the sequence's first run: those of the sequences before it come first
   for (int s = 0; s < seq; ++s) {
@@ -332,20 +335,31 @@ __global__ void __launch_bounds__(THREADS) chunk_carry_kernel(ChunkArgs c) {
   const size_t per_run = static_cast<size_t>(a.heads) * a.dim * a.vdim;
   float* local = c.chunk_state + (static_cast<size_t>(run) * a.heads + head) * a.dim * a.vdim + element;
   const int runs = (length + CHUNK - 1) / CHUNK;
-  float held = *mine;
-  for (int r = 0; r < runs; r += 4) {
-    float add[4];
+  float held[VEC];
+  if constexpr (VEC == 4) load4<float>(mine, held);
+  else held[0] = *mine;
+  for (int r = 0; r < runs; r += CARRY_AHEAD) {
+    float add[CARRY_AHEAD][VEC];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) add[i] = r + i < runs ? local[(r + i) * per_run] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < CARRY_AHEAD; ++i)
       if (r + i < runs) {
-        local[(r + i) * per_run] = held;             // S before this run: what `finish` reads
+        if constexpr (VEC == 4) load4<float>(local + (r + i) * per_run, add[i]);
+        else add[i][0] = local[(r + i) * per_run];
+      }
+#pragma unroll
+    for (int i = 0; i < CARRY_AHEAD; ++i)
+      if (r + i < runs) {
+        float* at = local + (r + i) * per_run;       // S before this run: what `finish` reads
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(at) = make_float4(held[0], held[1], held[2], held[3]);
+        else *at = held[0];
         const int tokens = min(CHUNK, length - (r + i) * CHUNK);
-        held = fmaf(tokens == CHUNK ? whole : int_power(d, tokens), held, add[i]);
+        const float keep = tokens == CHUNK ? whole : int_power(d, tokens);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) held[e] = fmaf(keep, held[e], add[i][e]);
       }
   }
-  *mine = held;
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(mine) = make_float4(held[0], held[1], held[2], held[3]);
+  else *mine = held[0];
 }
 
 // grid (column groups of `span`, heads, runs): o_t += d^(t - a + 1) S_before^T q_t, 64 columns at a time.
@@ -421,7 +435,10 @@ __global__ void __launch_bounds__(THREADS) chunk_finish_kernel(ChunkArgs c) {
 }
 
 // ---- norm_gate ------------------------------------------------------------------------------------------------
-template <typename T>
+// grid (rows, parts): a row's columns are shared among `parts` blocks (few rows fill the device all the same); with
+// a weight every block forms the row's sum of squares itself, in the same order.
+// VEC = 4: 16-byte accesses (the width, the gate's first column and the fused row's width multiples of four).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(THREADS) norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ gates,
                                                             int partials, long long partial_stride, int row_width, int gate_at,
                                                             const float* __restrict__ weight, float eps, T* __restrict__ out,
@@ -429,84 +446,114 @@ __global__ void __launch_bounds__(THREADS) norm_gate_kernel(const float* __restr
   __shared__ float scratch[33];
   let_dependents_start();
   wait_for_previous();
-  const int row = blockIdx.x;
+  const int row = blockIdx.x, groups = width / VEC;
   const float* src = x + static_cast<size_t>(row) * width;
   float gain = 1.0f;
   if (weight != nullptr) {
     float sq = 0.f;
-    for (int i = threadIdx.x; i < width; i += THREADS) sq = fmaf(src[i], src[i], sq);
+    for (int g = threadIdx.x; g < groups; g += THREADS) {
+      float v[VEC];
+      if constexpr (VEC == 4) load4<float>(src + g * 4, v);
+      else v[0] = src[g];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) sq = fmaf(v[e], v[e], sq);
+    }
     gain = 1.0f / sqrtf(block_sum(sq, scratch) / static_cast<float>(width) + eps);
   }
-  for (int i = threadIdx.x; i < width; i += THREADS) {
-    float v = src[i];
-    if (weight != nullptr) v = v * gain * weight[i];
-    if (gates != nullptr) {
-      const float g = sum_partials(gates + static_cast<size_t>(row) * row_width + gate_at + i, partial_stride, partials);
-      v = v / (1.0f + expf(-g));
+  const int each = (groups + gridDim.y - 1) / gridDim.y;
+  const int begin = blockIdx.y * each, end = min(groups, begin + each);
+  for (int g = begin + threadIdx.x; g < end; g += THREADS) {
+    const int i = g * VEC;
+    float v[VEC], w[VEC], gate[VEC];
+    if constexpr (VEC == 4) {
+      load4<float>(src + i, v);
+      if (weight != nullptr) load4<float>(weight + i, w);
+      if (gates != nullptr) sum_partials4(gates + static_cast<size_t>(row) * row_width + gate_at + i, partial_stride, partials, gate);
+    } else {
+      v[0] = src[i];
+      if (weight != nullptr) w[0] = weight[i];
+      if (gates != nullptr) gate[0] = sum_partials(gates + static_cast<size_t>(row) * row_width + gate_at + i, partial_stride, partials);
     }
-    out[static_cast<size_t>(row) * width + i] = from_float<T>(v);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      if (weight != nullptr) v[e] = v[e] * gain * w[e];
+      if (gates != nullptr) v[e] = v[e] / (1.0f + expf(-gate[e]));
+    }
+    T* dst = out + static_cast<size_t>(row) * width + i;
+    if constexpr (VEC == 4) store4<T>(dst, v);
+    else dst[0] = from_float<T>(v[0]);
   }
 }
 
 // ---- latent_rope_store ------------------------------------------------------------------------------------------
 // fused row: heads x [rank | rot] queries, then [rank | rot] of the token itself.  Inside a rotated part, dimension i
 // pairs with i + rot/2 and turns by position * inv_freq[i]; cos and sin are multiplied by `gain`.
+// grid (tokens, parts): the token's units (query head 0 .. heads - 1, then its own page row) are shared among
+// `parts` blocks, unit blockIdx.y, blockIdx.y + parts, ...  The rotation's sines and cosines depend on the token
+// alone: a block forms them once.
 template <typename T>
 __global__ void __launch_bounds__(THREADS) latent_rope_store_kernel(
     const float* __restrict__ fused, int partials, long long partial_stride, int row_width, const float* __restrict__ latent_weight,
     float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq, float gain, T* __restrict__ q_out,
     T* __restrict__ cache, const int* __restrict__ slots, int heads, int rank, int rot, int padded, long long num_slots) {
-  extern __shared__ __align__(16) float latent[];   // [rank]
+  extern __shared__ __align__(16) float latent[];   // [rank], then cos and sin times the gain [rot / 2] each
   __shared__ float scratch[33];
   let_dependents_start();
   wait_for_previous();
   const int token = blockIdx.x, half = rot / 2, each = rank + rot;
+  float* cos_s = latent + rank;
+  float* sin_s = cos_s + half;
   const float* row = fused + static_cast<size_t>(token) * row_width;
   const float position = static_cast<float>(positions[token]);
-  // queries: the latent-space part is cast, the rotated part turned
-  for (int i = threadIdx.x; i < heads * padded; i += THREADS) {
-    const int head = i / padded, e = i - head * padded;
-    float v = 0.f;
-    if (e < rank) {
-      v = sum_partials(row + head * each + e, partial_stride, partials);
-    } else if (e < each) {
-      const int r = e - rank, pair = r < half ? r : r - half;
-      const float angle = position * inv_freq[pair];
-      float s, c;
-      sincosf(angle, &s, &c);
-      const float lo = sum_partials(row + head * each + rank + pair, partial_stride, partials);
-      const float hi = sum_partials(row + head * each + rank + pair + half, partial_stride, partials);
-      v = r < half ? (lo * c - hi * s) * gain : (hi * c + lo * s) * gain;
-    }
-    q_out[static_cast<size_t>(token) * heads * padded + i] = from_float<T>(v);
+  for (int i = threadIdx.x; i < half; i += THREADS) {
+    float sn, cs;
+    sincosf(position * inv_freq[i], &sn, &cs);
+    cos_s[i] = cs * gain;
+    sin_s[i] = sn * gain;
   }
-  if (cache == nullptr) return;
-  long long slot = slots[token];
-  if (slot < 0 || slot >= num_slots) slot = -1;
-  const float* own = row + heads * each;
-  float sq = 0.f;
-  for (int i = threadIdx.x; i < rank; i += THREADS) {
-    const float v = sum_partials(own + i, partial_stride, partials);
-    latent[i] = v;
-    sq = fmaf(v, v, sq);
-  }
-  const float unit = 1.0f / sqrtf(block_sum(sq, scratch) / static_cast<float>(rank) + eps);
-  if (slot < 0) return;
-  T* dst = cache + static_cast<size_t>(slot) * padded;
-  for (int e = threadIdx.x; e < padded; e += THREADS) {
-    float v = 0.f;
-    if (e < rank) {
-      v = latent[e] * unit * latent_weight[e];
-    } else if (e < each) {
-      const int r = e - rank, pair = r < half ? r : r - half;
-      const float angle = position * inv_freq[pair];
-      float s, c;
-      sincosf(angle, &s, &c);
-      const float lo = sum_partials(own + rank + pair, partial_stride, partials);
-      const float hi = sum_partials(own + rank + pair + half, partial_stride, partials);
-      v = r < half ? (lo * c - hi * s) * gain : (hi * c + lo * s) * gain;
+  __syncthreads();
+  for (int unit = blockIdx.y; unit <= heads; unit += gridDim.y) {
+    const float* own = row + unit * each;
+    if (unit < heads) {   // a query head: the latent-space part is cast, the rotated part turned
+      T* dst = q_out + (static_cast<size_t>(token) * heads + unit) * padded;
+      for (int e = threadIdx.x; e < padded; e += THREADS) {
+        float v = 0.f;
+        if (e < rank) {
+          v = sum_partials(own + e, partial_stride, partials);
+        } else if (e < each) {
+          const int r = e - rank, pair = r < half ? r : r - half;
+          const float lo = sum_partials(own + rank + pair, partial_stride, partials);
+          const float hi = sum_partials(own + rank + pair + half, partial_stride, partials);
+          v = r < half ? lo * cos_s[pair] - hi * sin_s[pair] : hi * cos_s[pair] + lo * sin_s[pair];
+        }
+        dst[e] = from_float<T>(v);
+      }
+      continue;
     }
-    dst[e] = from_float<T>(v);
+    if (cache == nullptr) return;
+    long long slot = slots[token];
+    if (slot < 0 || slot >= num_slots) slot = -1;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < rank; i += THREADS) {
+      const float v = sum_partials(own + i, partial_stride, partials);
+      latent[i] = v;
+      sq = fmaf(v, v, sq);
+    }
+    const float unit_gain = 1.0f / sqrtf(block_sum(sq, scratch) / static_cast<float>(rank) + eps);
+    if (slot < 0) return;
+    T* dst = cache + static_cast<size_t>(slot) * padded;
+    for (int e = threadIdx.x; e < padded; e += THREADS) {
+      float v = 0.f;
+      if (e < rank) {
+        v = latent[e] * unit_gain * latent_weight[e];
+      } else if (e < each) {
+        const int r = e - rank, pair = r < half ? r : r - half;
+        const float lo = sum_partials(own + rank + pair, partial_stride, partials);
+        const float hi = sum_partials(own + rank + pair + half, partial_stride, partials);
+        v = r < half ? lo * cos_s[pair] - hi * sin_s[pair] : hi * cos_s[pair] + lo * sin_s[pair];
+      }
+      dst[e] = from_float<T>(v);
+    }
   }
 }
 
@@ -539,6 +586,12 @@ __global__ void __launch_bounds__(THREADS) concat_cast_kernel(float* __restrict_
 }
 
 }  // namespace decay
+
+// Blocks a row of work is shared among, at most `most`: few rows are spread until the blocks fill the device twice.
+static int shrike_spread(int rows, int most) {
+  const int wanted = (2 * shrike_device().sm_count + rows - 1) / rows;
+  return wanted < 1 ? 1 : (wanted > most ? most : wanted);
+}
 
 // Runs of CHUNK tokens a batch of `n` tokens in `seqs` sequences makes at most.
 SHRIKE_API long long shrike_decay_scan_chunks(int n, int seqs) { return n / decay::CHUNK + seqs; }
@@ -602,8 +655,12 @@ SHRIKE_API int shrike_decay_scan(const float* fused, int partials, long long par
     const dim3 per_chunk((vdim + c.span - 1) / c.span, heads, chunks);
     err = launch_dependent(chunk_local_kernel, per_chunk, dim3(THREADS), local_smem, stream, c);
     if (err != cudaSuccess) return static_cast<int>(err);
-    const dim3 per_seq((dim * vdim + THREADS - 1) / THREADS, heads, num_seqs);
-    err = launch_dependent(chunk_carry_kernel, per_seq, dim3(THREADS), 0, stream, c);
+    // four elements a thread where every head's state and every run's addition start on 16 bytes
+    const bool carry_wide = (dim * vdim) % 4 == 0 && state_stride % 4 == 0;
+    const int carry_threads = carry_wide ? dim * vdim / 4 : dim * vdim;
+    const dim3 per_seq((carry_threads + THREADS - 1) / THREADS, heads, num_seqs);
+    err = carry_wide ? launch_dependent(chunk_carry_kernel<4>, per_seq, dim3(THREADS), 0, stream, c)
+                     : launch_dependent(chunk_carry_kernel<1>, per_seq, dim3(THREADS), 0, stream, c);
     if (err != cudaSuccess) return static_cast<int>(err);
     err = launch_dependent(chunk_finish_kernel, per_chunk, dim3(THREADS), finish_smem, stream, c);
     if (err != cudaSuccess) return static_cast<int>(err);
@@ -616,9 +673,15 @@ SHRIKE_API int shrike_norm_gate(const float* x, const float* gates, int partials
                                 cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (width <= 0) return SHRIKE_BAD_ARGUMENT;
-#define SHRIKE_NORM_GATE(T)                                                                                              \
-  launch_dependent(decay::norm_gate_kernel<T>, dim3(n), dim3(decay::THREADS), 0, stream, x, gates, partials, partial_stride, \
-                   row_width, gate_at, weight, eps, static_cast<T*>(out), width)
+  const auto on16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool wide = width % 4 == 0 && on16(x) && on16(out) && on16(weight) &&
+                    (gates == nullptr || (on16(gates) && gate_at % 4 == 0 && row_width % 4 == 0 && partial_stride % 4 == 0));
+  const int parts = shrike_spread(n, ((wide ? width / 4 : width) + decay::THREADS - 1) / decay::THREADS);
+#define SHRIKE_NORM_GATE(T)                                                                                                \
+  (wide ? launch_dependent(decay::norm_gate_kernel<T, 4>, dim3(n, parts), dim3(decay::THREADS), 0, stream, x, gates, partials, \
+                           partial_stride, row_width, gate_at, weight, eps, static_cast<T*>(out), width)                     \
+        : launch_dependent(decay::norm_gate_kernel<T, 1>, dim3(n, parts), dim3(decay::THREADS), 0, stream, x, gates, partials, \
+                           partial_stride, row_width, gate_at, weight, eps, static_cast<T*>(out), width))
   if (dtype == SHRIKE_F32) SHRIKE_NORM_GATE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_NORM_GATE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;
@@ -632,9 +695,10 @@ SHRIKE_API int shrike_latent_rope_store(const float* fused, int partials, long l
                                         int rank, int rot, int padded, long long num_slots, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (heads <= 0 || rank <= 0 || rot < 2 || rot % 2 || padded < rank + rot) return SHRIKE_BAD_ARGUMENT;
-  const size_t smem = static_cast<size_t>(rank) * sizeof(float);
+  const size_t smem = static_cast<size_t>(rank + rot) * sizeof(float);
+  const int parts = shrike_spread(n, heads + 1);
 #define SHRIKE_LATENT_ROPE(T)                                                                                          \
-  launch_dependent(decay::latent_rope_store_kernel<T>, dim3(n), dim3(decay::THREADS), smem, stream, fused, partials,     \
+  launch_dependent(decay::latent_rope_store_kernel<T>, dim3(n, parts), dim3(decay::THREADS), smem, stream, fused, partials, \
                    partial_stride, row_width, latent_weight, eps, positions, inv_freq, gain, static_cast<T*>(q_out),     \
                    static_cast<T*>(cache), slots, heads, rank, rot, padded, num_slots)
   if (dtype == SHRIKE_F32) SHRIKE_LATENT_ROPE(float);
