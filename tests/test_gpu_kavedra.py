@@ -159,14 +159,17 @@ def test_first_tokens_of_a_sequence(tmp_path_factory, key, dtype):
 
 @pytest.mark.parametrize("key", ["B", "D"])
 def test_a_request_in_company_equals_itself_alone(tmp_path_factory, key):
-    """float32: the logits of a position change by rounding at most with the cutting and the company."""
-    folder, requests, _, scale, _ = reference(key, "float32", tmp_path_factory)
+    """float32: the logits of a position change by rounding at most with the cutting and the company.  Rounding is
+    1e-5 of the logits' spread, or, at a position where the sharpened weights amplify it (the whole prompt's own
+    distance from the float64 oracle shows which), three times what it does to the whole prompt there."""
+    folder, requests, want, scale, _ = reference(key, "float32", tmp_path_factory)
     whole, _ = replay(folder, "float32", whole_trace(requests))
     mixed, _ = replay(folder, "float32", mixed_trace(requests, seed=3), poison=True)
     cut, _ = replay(folder, "float32", portions_trace(requests, [2, 9, 2, 33, 64]))
     for ident in requests:
-        assert distance(mixed[ident], whole[ident], scale).max() < 1e-5
-        assert distance(cut[ident], whole[ident], scale).max() < 1e-5
+        bound = np.maximum(1e-5, 3.0 * distance(whole[ident], want[ident], scale))
+        assert (distance(mixed[ident], whole[ident], scale) <= bound).all()
+        assert (distance(cut[ident], whole[ident], scale) <= bound).all()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
