@@ -57,7 +57,7 @@ KAVEDRA_A = {
 KAVEDRA_B = {
     "architecture": "Kavedra", "width": 128, "vocab": 300, "norm": {"eps": 1e-6},
     "layers": [
-        _with(_attention(2, 1, 64, 64, 0.12, (64, 500000.0)), 192),
+        _with(_attention(2, 1, 64, 64, 0.12, (64, 400000.0)), 192),
         _with(_latent(2, 32, 16, 64, 48, 0.15, 100.0), 96),
         _with(_lightning(1, 64, 64, (0.97,)), 160),
         _with(_attention(4, 4, 64, 32, 0.1, (32, 100.0)), None),
@@ -79,15 +79,15 @@ KAVEDRA_C = {
     ],
 }
 
-# heads of 128 and a latent whose page row is 128 wide; the repeated layers in the middle, two passes, holding all three
-# mixers; a long window
+# heads of 128 and a latent whose page row is 128 wide; the repeated layers in the middle, three passes, holding all
+# three mixers; a long window
 KAVEDRA_D = {
     "architecture": "Kavedra", "width": 64, "vocab": 151, "norm": {"eps": 1e-6}, "logit_scale": 1.5,
-    "loop": {"start": 1, "stop": 4, "times": 2},
+    "loop": {"start": 1, "stop": 4, "times": 3},
     "layers": [
-        _with(_lightning(2, 16, 16, (0.999, 0.7)), 96),
+        _with(_lightning(2, 16, 16, (0.9995, 0.7)), 96),
         _with(_attention(2, 1, 128, 128, 0.09, (64, 10000.0)), 32),
-        _with(_latent(2, 64, 32, 32, 96, 0.1, 50000.0, window=130, scaling=(8.0, 128, 16.0, 1.0)), 48),
+        _with(_latent(2, 64, 16, 32, 112, 0.1, 30000.0, window=130, scaling=(8.0, 128, 16.0, 1.0)), 48),
         _with(_lightning(1, 48, 32, (0.95,)), None),
         _with(_attention(4, 2, 32, 16, 0.2, (32, 300.0)), 40),
     ],

@@ -51,7 +51,7 @@ def run_scan(ops, fused, decays, state, slot, cuts, heads, dim, vdim, partials=1
 
 
 @pytest.mark.parametrize("heads,dim,vdim,decays", [
-    (2, 64, 32, (0.6, 0.999)), (3, 16, 24, (0.5, 1.0, 0.93)), (1, 64, 64, (0.97,)), (2, 40, 8, (0.3, 0.8)), (3, 8, 40, (0.9, 0.99, 0.6)),
+    (2, 64, 48, (0.6, 0.9995)), (3, 16, 24, (0.5, 1.0, 0.93)), (1, 64, 64, (0.97,)), (2, 40, 8, (0.3, 0.8)), (3, 8, 40, (0.9, 0.99, 0.6)),
     (1, 128, 128, (0.995,)), (2, 256, 96, (0.9, 1.0)), (2, 96, 200, (0.99, 0.7)), (1, 1, 1, (0.5,)), (2, 5, 3, (1.0, 0.25))])
 def test_decayed_scan_whole_in_portions_and_token_by_token(heads, dim, vdim, decays):
     ops = cuda_ops(torch.float32)
@@ -158,11 +158,11 @@ def halves(x, dims, first=0):
     return out
 
 
-STRETCHES = [None, (8.0, 512, 32.0, 1.0), (4.0, 64, 8.0, 2.0), (2.0, 4, 1000.0, 0.0001)]
+STRETCHES = [None, (8.0, 1024, 32.0, 1.0), (4.0, 64, 8.0, 2.0), (2.0, 4, 1000.0, 0.0001)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,rank,rot,partials,stretch", [(4, 96, 32, 1, 1), (3, 40, 8, 3, 2), (2, 12, 2, 1, 3), (1, 20, 4, 2, 0),
+@pytest.mark.parametrize("heads,rank,rot,partials,stretch", [(4, 80, 32, 1, 1), (3, 40, 8, 3, 2), (2, 12, 2, 1, 3), (1, 20, 4, 2, 0),
                                                              (2, 48, 16, 1, 0), (16, 512, 64, 1, 1)])
 def test_latent_is_normed_rotated_and_stored(dtype, heads, rank, rot, partials, stretch):
     ops = cuda_ops(dtype)
@@ -212,3 +212,120 @@ def test_latent_is_normed_rotated_and_stored(dtype, heads, rank, rot, partials, 
     ops.latent_rope_store(stack, weight.to(DEV), 1e-5, positions.to(DEV), rotation.inv_freq, rotation.gain, again, None,
                           slots.to(DEV), heads, rank, rot, padded)
     assert torch.equal(again, q_out)
+
+
+# ------------------------------------------------------------------ attention with softmax sinks
+def attend_with_sinks(ops, dtype, sequences, page, heads, kv_heads, dim, scale, window, sinks, shared_plane=False):
+    case = paged(dtype, sequences, page, kv_heads, dim, shared_plane)
+    out = torch.full_like(case["q"], float("nan"))
+    ops.paged_attention(case["q"], case["keys"], case["values"], case["table"], case["q_start"], case["ctx_len"], case["seq_of"],
+                        heads, kv_heads, dim, scale, window, out, max_q_len=max(case["q_lens"]), max_ctx_len=max(case["ctx_lens"]),
+                        min_q_len=min(case["q_lens"]), q_lens=case["q_lens"], sinks=sinks.float().to(DEV))
+    ops.check_status()
+    want = []
+    for q, k, v, q_len in sequences:
+        ctx = len(k)
+        r = lambda t: t.to(dtype).double()   # noqa: E731  the oracle sees the stored values
+        want.append(pk.attend(r(q[ctx - q_len:]), r(k), r(v), scale, sinks.double(), window, first_position=ctx - q_len))
+    return out, torch.cat(want).reshape(out.shape)
+
+
+def random_sequences(lengths, heads, kv_heads, dim, seed, spread=1.5):
+    sequences = []
+    for s, (ctx, q_len) in enumerate(lengths):
+        g = torch.Generator().manual_seed(seed + s)
+        sequences.append((torch.randn(ctx, heads, dim, generator=g) * spread, torch.randn(ctx, kv_heads, dim, generator=g),
+                          torch.randn(ctx, kv_heads, dim, generator=g), q_len))
+    return sequences
+
+
+def spread_sinks(heads):
+    """From a sink that takes nearly all of the weight to one that takes none."""
+    return torch.linspace(7.0, -30.0, heads)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window", [(4, 2, 32, 8, None), (3, 3, 48, 5, 37), (8, 1, 64, 16, None), (6, 2, 16, 16, 9),
+                                                            (2, 1, 256, 16, 70), (3, 1, 272, 8, None)])
+def test_sinks_in_single_tokens_and_portions(dtype, heads, kv_heads, dim, page, window):
+    """Every denominator holds exp(sink): single tokens (few and many keys, so split and not), portions beside them, the
+    first token of a sequence (one key against the sink), heads wider than the tensor-core kernels take."""
+    ops = cuda_ops(dtype)
+    sinks = spread_sinks(heads)
+    lengths = [(1, 1), (40, 1), (130, 1), (21, 2), (100, 37), (300, 129), (64, 64), (33, 1), (200, 3), (900, 1)]
+    sequences = random_sequences(lengths, heads, kv_heads, dim, 150)
+    got, want = attend_with_sinks(ops, dtype, sequences, page, heads, kv_heads, dim, dim ** -0.5 * 2, window, sinks)
+    close(got, want, TOL[dtype], "attention with sinks")
+    without = pk.attend(sequences[4][0][-37:].double(), sequences[4][1].double(), sequences[4][2].double(), dim ** -0.5 * 2, None, window, 63)
+    with_sinks = pk.attend(sequences[4][0][-37:].double(), sequences[4][1].double(), sequences[4][2].double(), dim ** -0.5 * 2, sinks.double(), window, 63)
+    assert (without - with_sinks).abs().max() > 0.3, "the oracle itself: these sinks matter"
+    singles = [(q, k, v, 1) for q, k, v, _ in sequences]     # the single-token kernel alone (other split and cluster shapes)
+    got, want = attend_with_sinks(ops, dtype, singles, page, heads, kv_heads, dim, dim ** -0.5 * 2, window, sinks)
+    close(got, want, TOL[dtype], "single tokens only")
+
+
+@pytest.mark.parametrize("tensor_core,splits", [(True, 0), (True, 3), (False, 0)])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,window", [(6, 2, 64, 16, 150), (4, 1, 128, 16, None), (2, 2, 128, 8, 300), (3, 3, 64, 32, None)])
+def test_sinks_on_the_tensor_core_portions_kernel(heads, kv_heads, dim, page, window, tensor_core, splits):
+    """Head sizes 64 and 128 take the tcgen05 kernel for portions: with and without it, and with a query tile's keys
+    shared by several CTAs (the sink must count once, not once a CTA), the same weights."""
+    ops = cuda_ops(torch.bfloat16)
+    ops.tensor_core_attention, ops.portion_splits = tensor_core, splits
+    sinks = spread_sinks(heads)
+    sequences = random_sequences([(700, 700), (130, 1), (500, 129), (300, 300), (64, 2), (1000, 37)], heads, kv_heads, dim, 170, spread=1.0)
+    got, want = attend_with_sinks(ops, torch.bfloat16, sequences, page, heads, kv_heads, dim, dim ** -0.5 * 3, window, sinks)
+    close(got, want, TOL[torch.bfloat16], "portions on the tensor cores with sinks")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_sink_above_every_score_leaves_almost_nothing(dtype):
+    """A sink far above the scores takes the weight: the outputs shrink by exp(score - sink), and a sink far below
+    changes nothing; a planted key far back still gets its share against the sink."""
+    ops = cuda_ops(dtype)
+    heads, kv_heads, dim, page = 2, 1, 32, 16
+    sequences = random_sequences([(600, 1), (600, 40)], heads, kv_heads, dim, 190, spread=0.3)
+    for q, k, v, _ in sequences:
+        k *= 0.1                    # the other keys' scores stay near 0
+        k[7] = 0.0
+        k[7, 0, 3] = 4.0
+        q[-1] = 0.0
+        q[-1, :, 3] = 5.0           # score 20 with key 7, about 0 with the others
+        v[7] = 50.0
+    sinks = torch.tensor([20.0, -40.0])
+    got, want = attend_with_sinks(ops, dtype, sequences, page, heads, kv_heads, dim, 1.0, None, sinks)
+    close(got, want, TOL[dtype] * 50, "a planted key against a sink")
+    for last in (got[0], got[-1]):
+        per_head = last.float().view(heads, dim).mean(-1)
+        assert 20 < per_head[0] < 30 and per_head[1] > 45, per_head   # half of the weight with the sink, all of it without
+
+
+# ------------------------------------------------------------------ the per-head product and the joined rows
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,heads,padded,vdim", [(1, 3, 48, 16), (37, 2, 64, 64), (130, 4, 128, 24), (5, 1, 32, 40)])
+def test_every_head_has_its_own_product(dtype, n, heads, padded, vdim):
+    ops = cuda_ops(dtype)
+    x = rnd(n, heads * padded, seed=1).to(dtype)
+    w = (rnd(heads, vdim, padded, seed=2) * 0.3).to(dtype)
+    out = torch.full((n, heads * vdim), float("nan"), dtype=torch.float32, device=DEV)
+    ops.head_linear(x.to(DEV), w.to(DEV), out, heads)
+    want = torch.einsum("nhp,hvp->nhv", x.double().view(n, heads, padded), w.double()).reshape(n, heads * vdim)
+    close(out, want, 1e-4 if dtype == torch.float32 else 2e-2, "per-head product")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,width,terms,partials", [(1, 64, 0, 1), (9, 96, 1, 1), (40, 72, 2, 3), (3, 128, 5, 2)])
+def test_pending_sums_are_added_and_the_rows_joined(dtype, n, width, terms, partials):
+    ops = cuda_ops(dtype)
+    resid, other = rnd(n, width, seed=1), rnd(n, width, seed=2)
+    pending, total = [], resid.double().clone()
+    for t in range(terms):
+        stack = rnd(partials, n, width, seed=10 + t)
+        scale = 0.5 + t
+        total += scale * stack.double().sum(0)
+        pending.append(((stack if partials > 1 else stack[0]).contiguous().to(DEV), scale))
+    held = resid.clone().to(DEV)
+    out = torch.full((n, 2 * width), float("nan"), dtype=dtype, device=DEV)
+    ops.concat_cast(held, pending, other.to(DEV), out)
+    close(held, total, 1e-5, "the residual holds the sums")
+    close(out[:, :width], total, TOL[dtype], "left half")
+    close(out[:, width:], other.double(), TOL[dtype], "right half")

@@ -52,7 +52,8 @@ def test_config_gives_each_layer_its_mixer_and_every_run_its_cache():
     once = parse_config(KAVEDRA_C)
     assert [(run.layer, run.enter) for run in once.order] == [(0, 0), (1, None), (2, None), (3, None), (4, None)]
     assert [(run.layer, run.cache, run.enter) for run in parse_config(KAVEDRA_D).order] == [
-        (0, 0, None), (1, 1, 0), (2, 2, None), (3, 3, None), (1, 4, 1), (2, 5, None), (3, 6, None), (4, 7, None)]
+        (0, 0, None), (1, 1, 0), (2, 2, None), (3, 3, None), (1, 4, 1), (2, 5, None), (3, 6, None), (1, 7, 2), (2, 8, None),
+        (3, 9, None), (4, 10, None)]
 
 
 def test_tensor_names_follow_the_layers():
@@ -100,7 +101,7 @@ def test_config_errors_name_the_key(change, text):
         parse_config(raw)
 
 
-@pytest.mark.parametrize("dims,base,stretch", [(8, 10000.0, (4.0, 64, 8.0, 2.0)), (32, 50000.0, (8.0, 512, 32.0, 1.0)),
+@pytest.mark.parametrize("dims,base,stretch", [(8, 10000.0, (4.0, 64, 8.0, 2.0)), (32, 40000.0, (8.0, 1024, 32.0, 1.0)),
                                                (2, 10.0, (2.0, 4, 1000.0, 0.0001)), (16, 100.0, None), (4, 50.0, (16.0, 32, 4.0, 1.0)),
                                                (64, 1e6, (40.0, 4096, 32.0, 1.0)), (6, 7.0, (3.0, 16, 1.0, 1.0))])
 def test_rotation_frequencies_and_gain(dims, base, stretch):
