@@ -47,7 +47,7 @@ from ..config.model_config import (
 from ..config.registry import Architecture, TensorNames, register_architecture
 from .vupitar import _need, _sub, run_order
 
-NORM_OFFSET = 1.0   # the norms' weights are stored around zero
+NORM_OFFSET = 1.0   # a norm's stored weight is its distance from one
 DEFAULT_MAX_POSITIONS = 1 << 20   # the design has no position table: nothing bounds a sequence but the pool
 
 

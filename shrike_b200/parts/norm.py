@@ -33,7 +33,7 @@ class RMSNorm:
         self.runtime = runtime
         self.weight = tensors["weight"].to(torch.float32).contiguous()
         offset = float(getattr(spec, "offset", 0.0))
-        if offset:   # a weight stored around zero: the sum is formed once, in 32-bit
+        if offset:   # the file holds the weight's distance from `offset`: the sum is formed once, in 32-bit
             self.weight = (self.weight + offset).contiguous()
 
     def add_norm(self, resid, delta, out_name="normed"):
