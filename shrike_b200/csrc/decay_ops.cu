@@ -113,6 +113,56 @@ __global__ void __launch_bounds__(THREADS) walk_kernel(ScanArgs a, int skip_long
   }
 }
 
+// The same walk for heads of so many rows that a thread's share of the state does not fit its registers: the state
+// stays in memory and every token reads and rewrites it (slow, and right; no model of the usual sizes comes here).
+__global__ void __launch_bounds__(THREADS) walk_in_memory_kernel(ScanArgs a, int skip_longer_than) {
+  extern __shared__ __align__(16) float shared[];
+  float* q_s = shared;                    // [dim]
+  float* k_s = q_s + a.dim;               // [dim]
+  float* v_s = k_s + a.dim;               // [slice]
+  float* part = v_s + a.slice;            // [groups][slice]
+  let_dependents_start();
+  wait_for_previous();
+  const int seq = blockIdx.z, head = blockIdx.y, first_col = blockIdx.x * a.slice;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int begin = a.q_start[seq], end = a.q_start[seq + 1];
+  if (skip_longer_than > 0 && end - begin > skip_longer_than) return;   // the chunked form serves it
+  const int cols = min(a.slice, a.vdim - first_col);
+  const int t = threadIdx.x;
+  const int col = t % a.slice, group = t / a.slice;
+  const bool active = group < a.groups && col < cols;
+  const float d = a.decays[head];
+  float* mine = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.state_stride + first_col + col;
+  const int q_at = head * a.dim, k_at = a.heads * a.dim + head * a.dim, v_at = 2 * a.heads * a.dim + head * a.vdim + first_col;
+  for (int token = begin; token < end; ++token) {
+    const float* row = a.fused + static_cast<size_t>(token) * a.row_width;
+    __syncthreads();   // the token before is done with q_s and part
+    for (int i = t; i < 2 * a.dim + cols; i += THREADS) {
+      const int at = i < a.dim ? q_at + i : (i < 2 * a.dim ? k_at + i - a.dim : v_at + i - 2 * a.dim);
+      q_s[i] = silu(sum_partials(row + at, a.partial_stride, a.partials));
+    }
+    __syncthreads();
+    if (active) {
+      const float v = v_s[col];
+      float sum = 0.f;
+      for (int r = group; r < a.dim; r += a.groups) {   // the same rows, in the same order, as the walk in registers
+        float* at = mine + static_cast<size_t>(r) * a.vdim;
+        const float held = fmaf(d, *at, k_s[r] * v);
+        *at = held;
+        sum = fmaf(held, q_s[r], sum);
+      }
+      part[group * a.slice + col] = sum;
+    }
+    __syncthreads();
+    if (t < cols) {
+      float total = 0.f;
+      for (int g = 0; g < a.groups; ++g) total += part[g * a.slice + t];
+      a.out[static_cast<size_t>(token) * a.heads * a.vdim + head * a.vdim + first_col + t] = total;
+    }
+  }
+}
+
 // ---- the chunked form ---------------------------------------------------------------------------------------
 // A sequence's new tokens are cut into runs of CHUNK from its first new token; only sequences that bring more than
 // `skip` tokens have runs, numbered sequence by sequence.  Every CTA finds its run from `q_start` alone (a walk over
@@ -616,15 +666,21 @@ SHRIKE_API int shrike_decay_scan(const float* fused, int partials, long long par
   if (a.groups > dim) a.groups = dim;
   const int slices = (vdim + a.slice - 1) / a.slice;
   const int rows = (dim + a.groups - 1) / a.groups;
-  if (rows > 64) return SHRIKE_BAD_ARGUMENT;
-  const bool chunked = chunk_state != nullptr && chunk_from > 0 && longest >= chunk_from;
+  // runs of tokens only where their shared memory fits; a head too tall for the walk's registers walks through memory
+  const size_t pitch = chunk_pitch(dim), dim4 = (static_cast<size_t>(dim) + 3) & ~static_cast<size_t>(3);
+  const size_t local_smem = (2 * CHUNK * pitch + static_cast<size_t>(CHUNK) * MAX_SLICE + CHUNK * SCORE_PITCH + CHUNK + 4) * sizeof(float);
+  const size_t finish_smem = (CHUNK * pitch + dim4 * MAX_SLICE + CHUNK + 4) * sizeof(float);
+  const size_t limit = shrike_device().max_smem;
+  const bool chunked = chunk_state != nullptr && chunk_from > 0 && longest >= chunk_from && local_smem <= limit && finish_smem <= limit;
   const int chunks = static_cast<int>(shrike_decay_scan_chunks(n, num_seqs));
   const int skip = chunked ? chunk_from - 1 : 0;
   const dim3 grid(slices, heads, num_seqs);
   const size_t smem = (2 * static_cast<size_t>(dim) + a.slice + static_cast<size_t>(a.groups) * a.slice) * sizeof(float);
+  if (smem > 48 * 1024) return SHRIKE_BAD_ARGUMENT;
   cudaError_t err;
 #define SHRIKE_WALK(R) err = launch_dependent(walk_kernel<R>, grid, dim3(THREADS), smem, stream, a, skip)
-  if (rows <= 8) SHRIKE_WALK(8);
+  if (rows > 64) err = launch_dependent(walk_in_memory_kernel, grid, dim3(THREADS), smem, stream, a, skip);
+  else if (rows <= 8) SHRIKE_WALK(8);
   else if (rows <= 16) SHRIKE_WALK(16);
   else if (rows <= 32) SHRIKE_WALK(32);
   else SHRIKE_WALK(64);
@@ -633,11 +689,6 @@ SHRIKE_API int shrike_decay_scan(const float* fused, int partials, long long par
   if (chunked) {
     ChunkArgs c;
     c.s = a; c.chunk_state = chunk_state; c.num_seqs = num_seqs; c.skip = skip;
-    const size_t pitch = chunk_pitch(dim), dim4 = (static_cast<size_t>(dim) + 3) & ~static_cast<size_t>(3);
-    const size_t local_smem = (2 * CHUNK * pitch + static_cast<size_t>(CHUNK) * MAX_SLICE + CHUNK * SCORE_PITCH + CHUNK + 4) * sizeof(float);
-    const size_t finish_smem = (CHUNK * pitch + dim4 * MAX_SLICE + CHUNK + 4) * sizeof(float);
-    const size_t limit = shrike_device().max_smem;
-    if (local_smem > limit || finish_smem > limit) return SHRIKE_BAD_ARGUMENT;
     static size_t raised_local = 0, raised_finish = 0;
     if (local_smem > raised_local) {
       if (cudaFuncSetAttribute(chunk_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(limit)) != cudaSuccess)

@@ -52,7 +52,8 @@ def run_scan(ops, fused, decays, state, slot, cuts, heads, dim, vdim, partials=1
 
 @pytest.mark.parametrize("heads,dim,vdim,decays", [
     (2, 64, 48, (0.6, 0.9995)), (3, 16, 24, (0.5, 1.0, 0.93)), (1, 64, 64, (0.97,)), (2, 40, 8, (0.3, 0.8)), (3, 8, 40, (0.9, 0.99, 0.6)),
-    (1, 128, 128, (0.995,)), (2, 256, 96, (0.9, 1.0)), (2, 96, 200, (0.99, 0.7)), (1, 1, 1, (0.5,)), (2, 5, 3, (1.0, 0.25))])
+    (1, 128, 128, (0.995,)), (2, 256, 96, (0.9, 1.0)), (2, 96, 200, (0.99, 0.7)), (1, 1, 1, (0.5,)), (2, 5, 3, (1.0, 0.25)),
+    (1, 320, 72, (0.98,)), (1, 520, 64, (0.9,)), (2, 600, 8, (0.99, 1.0))])
 def test_decayed_scan_whole_in_portions_and_token_by_token(heads, dim, vdim, decays):
     ops = cuda_ops(torch.float32)
     n = 200
