@@ -40,6 +40,8 @@ class KVGroupSpec:
     planes: int = 2   # tensors a token holds in a page: keys and values, or one that serves as both
     # positions cut into runs of `chunk`, counted from 0: a query sees the keys of its own run only
     chunk: int | None = None
+    # with a window: the sequence's first `keep_first` keys stay visible, so their pages are never given back
+    keep_first: int = 0
 
     @property
     def span(self) -> int | None:
@@ -163,7 +165,7 @@ class CacheManager:
     def portion_limit(self) -> int | None:
         """The longest portion one request can be fed in a step, whatever else is free: a group
         with a window must hold the window and the portion at once (None: no such bound)."""
-        limits = [max(1, (pool.count - 2) * self.page_size - group.span + 2)
+        limits = [max(1, (pool.count - 2 - self.blocks_for(group.keep_first)) * self.page_size - group.span + 2)
                   for pool, group in zip(self.pools, self.groups) if group.span is not None]
         return min(limits) if limits else None
 
@@ -178,7 +180,8 @@ class CacheManager:
         """Pages per group a request of `tokens` may hold at once when it is fed at most `portion`
         tokens a step (None: all at once).  A group with a window holds the pages that the
         window and the portion in flight touch, whatever the request's length."""
-        return [pages_in_flight(self.blocks_for(tokens), group.span, min(portion or tokens, tokens), self.page_size)
+        return [pages_in_flight(self.blocks_for(tokens), group.span, min(portion or tokens, tokens), self.page_size,
+                                group.keep_first)
                 for group in self.groups]
 
     # ---- a request's life ----------------------------------------------------
@@ -239,7 +242,8 @@ class CacheManager:
                 continue
             first_needed = group.first_needed(num_computed)
             passed = min(max(0, first_needed // self.page_size), table.length)
-            for index in range(table.released, passed):
+            kept = self.blocks_for(group.keep_first)   # the pages of the keys that stay visible are held to the end
+            for index in range(max(table.released, kept), passed):
                 pool.give_back(int(table.pages[index]))
                 table.pages[index] = -1
                 given += 1
@@ -261,13 +265,14 @@ class CacheManager:
         cache.live = False
 
 
-def pages_in_flight(whole: int, window: int | None, portion: int, page_size: int) -> int:
+def pages_in_flight(whole: int, window: int | None, portion: int, page_size: int, keep_first: int = 0) -> int:
     """Pages one request holds at most in a group: all `whole` of them, or, with a window (or chunks of
     that many positions, whose queries never see further back than a window of the chunk's size), those
-    from the first key the portion's first query still sees to the portion's last token."""
+    from the first key the portion's first query still sees to the portion's last token, and those of the
+    `keep_first` keys that stay visible."""
     if window is None:
         return whole
-    return min(whole, (window + portion - 2) // page_size + 2)
+    return min(whole, (window + portion - 2) // page_size + 2 + -(-keep_first // page_size))
 
 
 def pages_per_group(groups, page_size: int, budget_bytes: int, bytes_per_page: list[int], max_slots: int,
@@ -275,7 +280,8 @@ def pages_per_group(groups, page_size: int, budget_bytes: int, bytes_per_page: l
     """Page counts for a budget of bytes: every group without a window gets the same count N, a
     group with a window at most what `max_slots` requests fed `max_portion` tokens a step can
     hold of it; N is as large as the budget allows."""
-    caps = [None if group.span is None else max_slots * pages_in_flight(1 << 40, group.span, max_portion, page_size)
+    caps = [None if group.span is None else
+            max_slots * pages_in_flight(1 << 40, group.span, max_portion, page_size, group.keep_first)
             for group in groups]
     capped: set[int] = set()
     while True:
@@ -295,6 +301,7 @@ def group_caches(needs: dict[int, object]) -> list[KVGroupSpec]:
     groups: dict[tuple, list[int]] = {}
     for cache_id in sorted(needs):
         need = needs[cache_id]
-        key = (need.num_kv_heads, need.head_dim, need.window, getattr(need, "planes", 2), getattr(need, "chunk", None))
+        key = (need.num_kv_heads, need.head_dim, need.window, getattr(need, "planes", 2), getattr(need, "chunk", None),
+               getattr(need, "keep_first", 0))
         groups.setdefault(key, []).append(cache_id)
     return [KVGroupSpec(tuple(ids), *key) for key, ids in groups.items()]

@@ -188,6 +188,20 @@ class GatedHeadAttentionSpec(PartSpec):
     head_gate: bool = False
     rotation: PartSpec | None = None
     sink: bool = False
+    # `qk_norm` "whole" (instead of True, the norm per head): q and k are each divided by the root mean square of
+    # their WHOLE projection, all heads at once, and scaled by a weight of the projection's size
+    # `conv` T: a causal convolution of T taps over time on every channel of q, k and v, right behind the
+    # projection (bias included) and before norm and rotation; the T - 1 latest projected values are state
+    conv: int | None = None
+    # `value_norm`: every value head is divided by its own root mean square (no weight) before it is cached
+    value_norm: bool = False
+    # `softcap` c: a score s becomes c tanh(s / c)
+    softcap: float | None = None
+    # `keep_first` n (with a window): the sequence's first n keys stay visible to every later query
+    keep_first: int = 0
+    # `own_kv` False: the layer has no key and value projections and attends over the keys and values another
+    # layer cached (the run order says whose)
+    own_kv: bool = True
     kind: str = field(init=False, default="gated_head_attention")
 
     def __post_init__(self):
@@ -195,6 +209,16 @@ class GatedHeadAttentionSpec(PartSpec):
             raise ConfigError(f"heads={self.num_heads} is not a multiple of kv_heads={self.num_kv_heads}")
         if self.window is not None and self.chunk is not None:
             raise ConfigError("an attention layer has a window or a chunk, not both")
+        if self.qk_norm not in (False, True, "whole"):
+            raise ConfigError(f"qk_norm {self.qk_norm!r}; known: False, True (per head), 'whole'")
+        if self.conv is not None and not 1 <= self.conv <= 32:
+            raise ConfigError(f"a short convolution has 1 to 32 taps, got {self.conv}")
+        if self.conv is not None and not self.own_kv:
+            raise ConfigError("a layer that reads another layer's keys and values has no convolution state of its own")
+        if self.softcap is not None and not self.softcap > 0:
+            raise ConfigError(f"softcap must be positive, got {self.softcap}")
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            raise ConfigError("keep_first goes with a window and is not negative")
         if self.rotary is not None and self.rotation is not None:
             raise ConfigError("an attention layer has `rotary` or `rotation`, not both")
         if self.rotation is not None and self.rotation.dims > self.head_dim:
@@ -221,6 +245,7 @@ class PairRotationSpec(PartSpec):
     base: float
     pairing: str = "halves"
     stretch: tuple | None = None
+    divide: float | None = None   # linear scaling: every f_i is divided by this
     kind: str = field(init=False, default="pair_rotation")
 
     def __post_init__(self):
@@ -232,6 +257,8 @@ class PairRotationSpec(PartSpec):
             raise ConfigError(f"a rotation's base must exceed 1, got {self.base}")
         if self.stretch is not None and (len(self.stretch) != 4 or not self.stretch[0] > 0):
             raise ConfigError("a rotation's stretch is (factor, original, fast, slow) with a positive factor")
+        if self.divide is not None and not self.divide > 0:
+            raise ConfigError(f"a rotation's frequencies are divided by a positive number, got {self.divide}")
 
 
 @dataclass(frozen=True)
@@ -291,6 +318,56 @@ class DecayLinearAttentionSpec(PartSpec):
             raise ConfigError(f"every decay lies in (0, 1], got {list(self.decays)}")
         if self.activation != "silu":
             raise ConfigError(f"linear attention activation {self.activation!r}; known: silu")
+
+
+@dataclass(frozen=True)
+class GatedLinearRecurrenceSpec(PartSpec):
+    """Linear attention in which the forget gate also decides what is written (the HGRN2 cell).  Per head, with
+    q = silu(Wq x) (dim), v = Wv x (vdim) and the gate f = lower + (1 - lower) * sigmoid(Wf x + b) per channel of q:
+
+        S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T  from S = 0;   o_t = S_t^T q_t   (no key, no scale)
+
+    Every head's output is divided by its root mean square and scaled by one weight of the head's size that all
+    heads share; the heads side by side are projected.  `lower_bound`: the model holds `lower` (one number a gate
+    channel); without it the bound is 0.  Gates, state and recurrence are 32-bit."""
+
+    width: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    eps: float
+    lower_bound: bool = True
+    kind: str = field(init=False, default="gated_linear_recurrence")
+
+
+@dataclass(frozen=True)
+class HyperConnectionSpec(PartSpec):
+    """How a sublayer's result y joins a residual of `streams` streams x_1 .. x_S, and how the sublayer reads them:
+    u = sum_s in[s] x_s is what the sublayer's norm sees; afterwards, all streams at once from the old ones,
+    x_t <- sum_s mix[s, t] x_s + out[t] * (scale * y), `scale` a learned vector over the width (`layer_scale`; else 1).
+    `learned` False: one stream's worth of constants (in = out = mix = 1), the ordinary residual sum."""
+
+    width: int
+    streams: int = 1
+    layer_scale: bool = False
+    learned: bool = True
+    kind: str = field(init=False, default="hyper_connection")
+
+    def __post_init__(self):
+        if not 1 <= self.streams <= 8:
+            raise ConfigError(f"a residual has 1 to 8 streams, got {self.streams}")
+        if not self.learned and self.streams != 1:
+            raise ConfigError("several residual streams need learned connections")
+
+
+@dataclass(frozen=True)
+class ResidualStreamsSpec(PartSpec):
+    """The residual as `streams` copies of the embedding's output that the layers' connections mix; what the final
+    norm sees is their sum."""
+
+    width: int
+    streams: int
+    kind: str = field(init=False, default="residual_streams")
 
 
 @dataclass(frozen=True)
@@ -365,11 +442,21 @@ class RoutedExpertsSpec(PartSpec):
     shared_intermediate: int | None = None
     shared_gate: bool = True
     renorm_eps: float = 1e-20
+    # `scoring` "sigmoid": an expert's score is the sigmoid of its own logit; `renormalise` False: the chosen experts
+    # keep their scores as weights; `weight_on` "input": an expert runs on weight * x instead of its output being
+    # multiplied, sum_e expert_e(w_e x)
+    scoring: str = "softmax"
+    renormalise: bool = True
+    weight_on: str = "output"
     kind: str = field(init=False, default="routed_experts")
 
     def __post_init__(self):
         if not 1 <= self.top <= self.experts:
             raise ConfigError(f"router: top={self.top} must lie in 1..experts={self.experts}")
+        if self.scoring not in ("softmax", "sigmoid"):
+            raise ConfigError(f"router scoring {self.scoring!r}; known: softmax, sigmoid")
+        if self.weight_on not in ("output", "input"):
+            raise ConfigError(f"an expert's weight sits on its output or its input, got {self.weight_on!r}")
 
 
 @dataclass(frozen=True)
@@ -487,6 +574,9 @@ class ModelConfig:
     head: PartSpec | None = None
     # what happens to the residual when a run opens a pass over repeated layers (`LayerRun.enter`)
     pass_entry: PartSpec | None = None
+    # a residual that is not one row a token (several streams): made from the embedding's output before the first
+    # layer, turned into the final norm's input after the last
+    residual: PartSpec | None = None
 
     def __post_init__(self):
         if self.embedding is None:

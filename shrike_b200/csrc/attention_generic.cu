@@ -55,7 +55,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ ctx_len, const int* __restrict__ seq_of_token,
                                int num_heads, int num_kv_heads, int page_size, int num_pages,
                                float scale, int window, float softcap, const float* __restrict__ slopes,
-                               const float* __restrict__ sinks, T* __restrict__ out, int num_tokens) {
+                               const float* __restrict__ sinks, T* __restrict__ out, int num_tokens, int keep_first) {
   __shared__ float q_shared[WARPS][D];
   let_dependents_start();
   wait_for_previous();
@@ -83,9 +83,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   float running_max = -INFINITY, running_sum = 0.f;
   const size_t row_stride = static_cast<size_t>(num_kv_heads) * D;
 
-  for (int base = first; base <= last; base += 32) {
+  // with a window, the sequence's first `keep_first` keys stay visible after the window has passed them: they are
+  // walked first, at their true positions, then the window's own keys
+  const int kept_end = window > 0 ? min(keep_first, first) : 0;
+  for (int part = kept_end > 0 ? 0 : 1; part < 2; ++part) {
+  const int part_first = part == 0 ? 0 : first, part_last = part == 0 ? kept_end - 1 : last;
+  for (int base = part_first; base <= part_last; base += 32) {
     const int key = base + lane;
-    const bool valid = key <= last;
+    const bool valid = key <= part_last;
     long long row = -1;
     if (valid) {
       const int block = key / page_size;
@@ -109,14 +114,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     }
     const float tile_max = warp_max(score);
     const float new_max = fmaxf(running_max, tile_max);
-    // new_max is finite: the query's own key is always present and valid
+    // the query's own key is always present and valid; a run of kept keys whose pages are all absent adds nothing
+    if (new_max == -INFINITY) continue;
     const float correction = expf(running_max - new_max);
     const float p = row >= 0 ? expf(score - new_max) : 0.f;
     running_sum = running_sum * correction + warp_sum(p);
     running_max = new_max;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[i] *= correction;
-    const int count = min(32, last - base + 1);
+    const int count = min(32, part_last - base + 1);
     for (int j = 0; j < count; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long row_j = __shfl_sync(0xffffffffu, row, j);
@@ -128,6 +134,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         if (d < D) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
       }
     }
+  }
   }
   T* out_row = out + (static_cast<size_t>(token) * num_heads + head) * D;
   // a sink: one more term of the denominator whose share of the weight attends to nothing (taken without `scale`).  The maximum moves to the larger
@@ -151,14 +158,16 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 SHRIKE_API int shrike_attention_head_dim() { return D; }
 
 // `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
-SHRIKE_API int shrike_paged_attention_generic_sinks(const void* q, const void* k_cache, const void* v_cache,
-                                                    const int* block_table, int max_blocks, const int* q_start,
-                                                    const int* ctx_len, const int* seq_of_token, int dtype,
-                                                    int num_tokens, int num_heads, int num_kv_heads,
-                                                    int page_size, int num_pages, float scale, int window,
-                                                    float softcap, const float* slopes, const float* sinks, void* out,
-                                                    cudaStream_t stream) {
+// `keep_first` (with a window): the sequence's first `keep_first` keys stay visible to every later query.
+SHRIKE_API int shrike_paged_attention_generic_kept(const void* q, const void* k_cache, const void* v_cache,
+                                                   const int* block_table, int max_blocks, const int* q_start,
+                                                   const int* ctx_len, const int* seq_of_token, int dtype,
+                                                   int num_tokens, int num_heads, int num_kv_heads,
+                                                   int page_size, int num_pages, float scale, int window,
+                                                   float softcap, const float* slopes, const float* sinks, int keep_first,
+                                                   void* out, cudaStream_t stream) {
   if (num_tokens <= 0) return SHRIKE_OK;
+  if (keep_first < 0) return SHRIKE_BAD_ARGUMENT;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0)
     return SHRIKE_BAD_ARGUMENT;
   const long long work = static_cast<long long>(num_tokens) * num_heads;
@@ -168,12 +177,24 @@ SHRIKE_API int shrike_paged_attention_generic_sinks(const void* q, const void* k
   paged_attention_generic_kernel<T><<<static_cast<int>(blocks), WARPS * 32, 0, stream>>>(           \
       static_cast<const T*>(q), static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),     \
       block_table, max_blocks, q_start, ctx_len, seq_of_token, num_heads, num_kv_heads, page_size,  \
-      num_pages, scale, window, softcap, slopes, sinks, static_cast<T*>(out), num_tokens)
+      num_pages, scale, window, softcap, slopes, sinks, static_cast<T*>(out), num_tokens, keep_first)
   if (dtype == SHRIKE_F32) SHRIKE_ATTN_CASE(float);
   else if (dtype == SHRIKE_BF16) SHRIKE_ATTN_CASE(__nv_bfloat16);
   else return SHRIKE_BAD_ARGUMENT;
 #undef SHRIKE_ATTN_CASE
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_generic_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                    const int* block_table, int max_blocks, const int* q_start,
+                                                    const int* ctx_len, const int* seq_of_token, int dtype,
+                                                    int num_tokens, int num_heads, int num_kv_heads,
+                                                    int page_size, int num_pages, float scale, int window,
+                                                    float softcap, const float* slopes, const float* sinks, void* out,
+                                                    cudaStream_t stream) {
+  return shrike_paged_attention_generic_kept(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, seq_of_token,
+                                             dtype, num_tokens, num_heads, num_kv_heads, page_size, num_pages, scale, window,
+                                             softcap, slopes, sinks, 0, out, stream);
 }
 
 SHRIKE_API int shrike_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,

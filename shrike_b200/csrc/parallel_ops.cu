@@ -138,13 +138,16 @@ struct HeadPrepArgs {
   const int* slots;       // [N]; -1: nothing is stored
   float* gate_out;        // [N][H] or null
   int n, heads, kv_heads, dim, vdim, padded, num_slots;
+  int whole_norm;         // 1: q and k are each divided by the root mean square of their WHOLE projection (all heads
+                          // at once) and q_weight / k_weight hold one number a column ([H D], [G D])
+  int value_norm;         // 1: every value head is divided by its own root mean square (no weight)
 };
 
 constexpr int PREP_WARPS = 4;
 
 template <typename T>
 __device__ __forceinline__ void head_prep_unit(const HeadPrepArgs& a, const float* row, int token, int unit, float* mine,
-                                               const float* cosines, const float* sines, int lane) {
+                                               const float* cosines, const float* sines, int lane, const float* whole) {
   const int q_cols = a.heads * a.dim, k_cols = a.kv_heads * a.dim, v_cols = a.kv_heads * a.vdim;
   if (unit == a.heads + 2 * a.kv_heads) {   // the gates: one number a head
     for (int h = lane; h < a.heads; h += 32) {
@@ -167,6 +170,8 @@ __device__ __forceinline__ void head_prep_unit(const HeadPrepArgs& a, const floa
     dst = static_cast<T*>(is_k ? a.keys : a.values) + (static_cast<size_t>(slot) * a.kv_heads + head) * a.padded;
   }
   const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+  if (a.whole_norm && weight != nullptr) weight += head * a.dim;
+  const bool normed = weight != nullptr || (!is_q && !is_k && a.value_norm);
   const int half = (is_q || is_k) && a.inv_freq != nullptr ? a.rot / 2 : 0;
   // four consecutive elements a lane, 16-byte accesses, where sizes and addresses allow
   const bool wide = (size & 3) == 0 && (a.padded & 3) == 0 && (first_col & 3) == 0 && (a.total & 3) == 0 && (a.stride & 3) == 0 &&
@@ -190,11 +195,12 @@ __device__ __forceinline__ void head_prep_unit(const HeadPrepArgs& a, const floa
         squares = __fmaf_rn(v[e], v[e], squares);
       }
     }
-    if (weight != nullptr) {
-      const float r = rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
+    if (normed) {
+      const float r = a.whole_norm && weight != nullptr ? whole[is_q ? 0 : 1]
+                                                        : rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
       for (int d = lane * 4; d < size; d += 128) {
-        float w[4];
-        load4<float>(weight + d, w);
+        float w[4] = {1.f, 1.f, 1.f, 1.f};
+        if (weight != nullptr) load4<float>(weight + d, w);
 #pragma unroll
         for (int e = 0; e < 4; ++e) mine[d + e] = mine[d + e] * r * w[e];
       }
@@ -223,9 +229,10 @@ __device__ __forceinline__ void head_prep_unit(const HeadPrepArgs& a, const floa
     mine[d] = v;
     squares = __fmaf_rn(v, v, squares);
   }
-  if (weight != nullptr) {
-    const float r = rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
-    for (int d = lane; d < size; d += 32) mine[d] = mine[d] * r * weight[d];
+  if (normed) {
+    const float r = a.whole_norm && weight != nullptr ? whole[is_q ? 0 : 1]
+                                                      : rsqrtf(warp_sum(squares) / static_cast<float>(size) + a.eps);
+    for (int d = lane; d < size; d += 32) mine[d] = mine[d] * r * (weight != nullptr ? weight[d] : 1.f);
   }
   __syncwarp();
   for (int d = lane; d < a.padded; d += 32) {
@@ -258,9 +265,30 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) head_prep_kernel(const HeadPr
   const float position = static_cast<float>(a.positions[token]);
   for (int i = threadIdx.x; i < table_half; i += blockDim.x) sincosf(__fmul_rn(position, a.inv_freq[i]), &sines[i], &cosines[i]);
   __syncthreads();
+  __shared__ float whole[2];      // whole_norm: 1 / rms of the token's whole q and k projections
+  __shared__ float whole_scratch[33];
+  if (a.whole_norm) {
+    // every block of a token forms both statistics itself: few tokens are spread over many blocks, and the row is
+    // read from the cache then
+    const int q_cols = a.heads * a.dim, k_cols = a.kv_heads * a.dim;
+    for (int which = 0; which < 2; ++which) {
+      const int first = which == 0 ? 0 : q_cols, count = which == 0 ? q_cols : k_cols;
+      const bool wanted = (which == 0 ? a.q_weight : a.k_weight) != nullptr && count > 0;
+      float squares = 0.f;
+      if (wanted)
+        for (int c = threadIdx.x; c < count; c += blockDim.x) {
+          float v = sum_partials(row + first + c, a.stride, a.partials);
+          if (a.bias != nullptr) v = __fadd_rn(v, a.bias[first + c]);
+          squares = __fmaf_rn(v, v, squares);
+        }
+      const float total = block_sum(squares, whole_scratch);
+      if (threadIdx.x == 0) whole[which] = wanted ? rsqrtf(total / static_cast<float>(count) + a.eps) : 1.f;
+    }
+    __syncthreads();
+  }
   float* mine = prep_shared + static_cast<size_t>(warp) * a.padded;
   for (int unit = blockIdx.y * PREP_WARPS + warp; unit < units; unit += gridDim.y * PREP_WARPS) {
-    head_prep_unit<T>(a, row, token, unit, mine, cosines, sines, lane);
+    head_prep_unit<T>(a, row, token, unit, mine, cosines, sines, lane, whole);
     __syncwarp();   // the warp's buffer is read across lanes until a head is stored
   }
 }
@@ -882,7 +910,8 @@ constexpr int ROUTE_GROUP = 8;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ shared_gate,
-                 float* __restrict__ weights, int n, int width, int experts, int top, int columns, float renorm_eps) {
+                 float* __restrict__ weights, int n, int width, int experts, int top, int columns, float renorm_eps,
+                 int sigmoid_scores, int renormalise) {
   extern __shared__ float route_shared[];   // [ROUTE_WARPS][rows] sums of the warps, then [rows] scores in the first row
   let_dependents_start();
   wait_for_previous();
@@ -944,11 +973,12 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
   const float shared_dot = rows > experts ? score[experts] : 0.f;
   float total = 0.f;
   for (int e = lane; e < experts; e += 32) {
-    const float p = expf(score[e] - best);
+    // an expert's score: its share of the softmax over all experts, or the sigmoid of its own logit
+    const float p = sigmoid_scores ? 1.0f / (1.0f + expf(-score[e])) : expf(score[e] - best);
     score[e] = p;
     total += p;
   }
-  total = warp_sum(total);
+  total = sigmoid_scores ? 1.f : warp_sum(total);
   __syncwarp();
   for (int e = lane; e < experts; e += 32) {
     score[e] = score[e] / total;
@@ -975,8 +1005,10 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
     }
     __syncwarp();
   }
-  const float inv = 1.0f / (chosen_sum + renorm_eps);
-  for (int e = lane; e < experts; e += 32) out[e] = out[e] * inv;
+  if (renormalise) {
+    const float inv = 1.0f / (chosen_sum + renorm_eps);
+    for (int e = lane; e < experts; e += 32) out[e] = out[e] * inv;
+  }
   if (columns > experts && lane == 0) out[experts] = shared_gate != nullptr ? 1.0f / (1.0f + expf(-shared_dot)) : 1.f;
 }
 
@@ -986,7 +1018,7 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 act_mul_blocks_kernel(const T* __restrict__ gate_up, const float* __restrict__ weights, T* __restrict__ out, int n, int inter,
-                      int experts, int each, int columns, int act, float limit) {
+                      int experts, int each, int columns, int act, float limit, int weight_input) {
   let_dependents_start();
   wait_for_previous();
   // VEC consecutive columns a thread (one 16-byte access each way when VEC > 1; the launcher sees to it that a
@@ -1009,7 +1041,12 @@ act_mul_blocks_kernel(const T* __restrict__ gate_up, const float* __restrict__ w
       } else {
         const Pack g = *reinterpret_cast<const Pack*>(in + c), u = *reinterpret_cast<const Pack*>(in + inter + c);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) r.v[j] = from_float<T>(__fmul_rn(act_times<T>(act, to_float(g.v[j]), to_float(u.v[j]), limit), share));
+        for (int j = 0; j < VEC; ++j) {
+          // the weight on the expert's INPUT reaches gate and up alike (both are linear in it): act(w g) (w u)
+          const float gate = to_float(g.v[j]), up = to_float(u.v[j]);
+          r.v[j] = from_float<T>(weight_input ? act_times<T>(act, __fmul_rn(share, gate), __fmul_rn(share, up), limit)
+                                              : __fmul_rn(act_times<T>(act, gate, up, limit), share));
+        }
       }
       *reinterpret_cast<Pack*>(o + c) = r;
     }
@@ -1063,18 +1100,21 @@ SHRIKE_API int shrike_tanh_norm(float* resid, const float* const* data, const in
   return shrike_launch_status();
 }
 
-SHRIKE_API int shrike_head_prep(const float* fused, int partials, long long stride, int total, const float* bias,
-                                const int* positions, const float* inv_freq, int rot, const float* q_weight,
-                                const float* k_weight, float eps, void* q_out, void* keys, void* values, const int* slots,
-                                float* gate_out, int dtype, int n, int heads, int kv_heads, int dim, int vdim, int padded,
-                                int num_slots, cudaStream_t stream) {
+// `whole_norm`: q and k over the root mean square of their whole projections, the weights one number a column.
+// `value_norm`: every value head over its own root mean square.  `kv_heads` 0: the projection holds queries alone
+// (a layer that reads another layer's keys and values).
+SHRIKE_API int shrike_head_prep_norms(const float* fused, int partials, long long stride, int total, const float* bias,
+                                      const int* positions, const float* inv_freq, int rot, const float* q_weight,
+                                      const float* k_weight, float eps, void* q_out, void* keys, void* values, const int* slots,
+                                      float* gate_out, int dtype, int n, int heads, int kv_heads, int dim, int vdim, int padded,
+                                      int num_slots, int whole_norm, int value_norm, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
-  if (heads < 1 || kv_heads < 1 || dim < 1 || vdim < 1 || padded < dim || padded < vdim || partials < 1 || rot < 0 ||
+  if (heads < 1 || kv_heads < 0 || dim < 1 || vdim < 1 || padded < dim || padded < vdim || partials < 1 || rot < 0 ||
       rot % 2 || rot > dim || padded > 8192)
     return SHRIKE_BAD_ARGUMENT;
   if (total < heads * dim + kv_heads * (dim + vdim) + (gate_out != nullptr ? heads : 0)) return SHRIKE_BAD_ARGUMENT;
   HeadPrepArgs a = {fused, stride, partials, total, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys,
-                    values, slots, gate_out, n, heads, kv_heads, dim, vdim, padded, num_slots};
+                    values, slots, gate_out, n, heads, kv_heads, dim, vdim, padded, num_slots, whole_norm, value_norm};
   const int units = heads + 2 * kv_heads + (gate_out != nullptr ? 1 : 0);
   // few tokens: a warp a unit, so that a step's heads are all under way at once; many: a block a token
   const int per_token = n >= 1024 ? 1 : (units + PREP_WARPS - 1) / PREP_WARPS;
@@ -1089,6 +1129,16 @@ SHRIKE_API int shrike_head_prep(const float* fused, int partials, long long stri
     launch_dependent(head_prep_kernel<__nv_bfloat16>, blocks, PREP_WARPS * 32, smem, stream, a);
   } else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_head_prep(const float* fused, int partials, long long stride, int total, const float* bias,
+                                const int* positions, const float* inv_freq, int rot, const float* q_weight,
+                                const float* k_weight, float eps, void* q_out, void* keys, void* values, const int* slots,
+                                float* gate_out, int dtype, int n, int heads, int kv_heads, int dim, int vdim, int padded,
+                                int num_slots, cudaStream_t stream) {
+  if (kv_heads < 1) return SHRIKE_BAD_ARGUMENT;
+  return shrike_head_prep_norms(fused, partials, stride, total, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out,
+                                keys, values, slots, gate_out, dtype, n, heads, kv_heads, dim, vdim, padded, num_slots, 0, 0, stream);
 }
 
 // Value columns a CTA of the scan takes: as many (at most 64) as let the state slice, the staged tokens and a
@@ -1190,24 +1240,33 @@ SHRIKE_API int shrike_matrix_memory_out(const float* numerator, const float* den
 
 // weights [N][columns], columns = experts (+ 1 when there is a shared expert: its gate, sigmoid(shared_gate . x), or 1
 // when shared_gate is null).
-SHRIKE_API int shrike_route_top(const void* x, int dtype, const float* router, const float* shared_gate, float* weights, int n,
-                                int width, int experts, int top, int columns, float renorm_eps, cudaStream_t stream) {
+// `sigmoid_scores`: an expert's score is the sigmoid of its logit instead of its softmax share; `renormalise` 0: the
+// chosen experts keep their scores as they are.
+SHRIKE_API int shrike_route_top_scores(const void* x, int dtype, const float* router, const float* shared_gate, float* weights, int n,
+                                       int width, int experts, int top, int columns, float renorm_eps, int sigmoid_scores,
+                                       int renormalise, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (experts < 1 || top < 1 || top > experts || experts > 1024 || (columns != experts && columns != experts + 1)) return SHRIKE_BAD_ARGUMENT;
   const unsigned blocks = static_cast<unsigned>(n);
   const size_t smem = static_cast<size_t>(ROUTE_WARPS) * (experts + 1) * sizeof(float);
   if (dtype == SHRIKE_F32)
     launch_dependent(route_top_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, static_cast<const float*>(x), router,
-                     shared_gate, weights, n, width, experts, top, columns, renorm_eps);
+                     shared_gate, weights, n, width, experts, top, columns, renorm_eps, sigmoid_scores, renormalise);
   else if (dtype == SHRIKE_BF16)
     launch_dependent(route_top_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream, static_cast<const __nv_bfloat16*>(x),
-                     router, shared_gate, weights, n, width, experts, top, columns, renorm_eps);
+                     router, shared_gate, weights, n, width, experts, top, columns, renorm_eps, sigmoid_scores, renormalise);
   else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
 }
 
-SHRIKE_API int shrike_act_mul_blocks(const void* gate_up, const float* weights, void* out, int dtype, int n, int inter, int experts,
-                                     int each, int columns, int act, float limit, cudaStream_t stream) {
+SHRIKE_API int shrike_route_top(const void* x, int dtype, const float* router, const float* shared_gate, float* weights, int n,
+                                int width, int experts, int top, int columns, float renorm_eps, cudaStream_t stream) {
+  return shrike_route_top_scores(x, dtype, router, shared_gate, weights, n, width, experts, top, columns, renorm_eps, 0, 1, stream);
+}
+
+// `weight_input` 1: an expert's weight multiplies its input, out = act(w gate) * (w up), instead of its output.
+SHRIKE_API int shrike_act_mul_blocks_at(const void* gate_up, const float* weights, void* out, int dtype, int n, int inter, int experts,
+                                        int each, int columns, int act, float limit, int weight_input, cudaStream_t stream) {
   if (n <= 0) return SHRIKE_OK;
   if (inter < 1 || experts < 1 || each < 1 || experts * each > inter || !known_activation(act)) return SHRIKE_BAD_ARGUMENT;
   if (experts * each < inter && columns != experts + 1) return SHRIKE_BAD_ARGUMENT;
@@ -1219,20 +1278,25 @@ SHRIKE_API int shrike_act_mul_blocks(const void* gate_up, const float* weights, 
     const dim3 grid(max(1, min(64, (groups + 255) / 256)), max(1, min(n, 65535)));
     if (vec)
       launch_dependent(act_mul_blocks_kernel<float, 4>, grid, 256, 0, stream, static_cast<const float*>(gate_up), weights,
-                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit);
+                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit, weight_input);
     else
       launch_dependent(act_mul_blocks_kernel<float, 1>, grid, 256, 0, stream, static_cast<const float*>(gate_up), weights,
-                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit);
+                       static_cast<float*>(out), n, inter, experts, each, columns, act, limit, weight_input);
   } else if (dtype == SHRIKE_BF16) {
     const bool vec = aligned && inter % wide_bf16 == 0 && each % wide_bf16 == 0;
     const int groups = vec ? inter / wide_bf16 : inter;
     const dim3 grid(max(1, min(64, (groups + 255) / 256)), max(1, min(n, 65535)));
     if (vec)
       launch_dependent(act_mul_blocks_kernel<__nv_bfloat16, 8>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
-                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit);
+                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit, weight_input);
     else
       launch_dependent(act_mul_blocks_kernel<__nv_bfloat16, 1>, grid, 256, 0, stream, static_cast<const __nv_bfloat16*>(gate_up),
-                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit);
+                       weights, static_cast<__nv_bfloat16*>(out), n, inter, experts, each, columns, act, limit, weight_input);
   } else return SHRIKE_BAD_ARGUMENT;
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_act_mul_blocks(const void* gate_up, const float* weights, void* out, int dtype, int n, int inter, int experts,
+                                     int each, int columns, int act, float limit, cudaStream_t stream) {
+  return shrike_act_mul_blocks_at(gate_up, weights, out, dtype, n, inter, experts, each, columns, act, limit, 0, stream);
 }

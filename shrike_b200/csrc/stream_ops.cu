@@ -1,0 +1,556 @@
+// Kernels for a decoder whose residual is several streams (hyper-connections), whose attention has a short causal
+// convolution over time behind its projections, and whose recurrent mixer lets one gate decide what a state forgets
+// and what it takes in.
+//
+//   stream_norm      the residual as S streams x_1 .. x_S of a token, [N][S][W] float32.  First the pending sublayer
+//                    result y (up to four pending sums, each a [N, W] array or a K-split stack with a scale, times a
+//                    layer scale [W]) joins them, all new streams from the old ones:
+//                        x_t <- sum_s mix[s][t] x_s + out[t] y
+//                    then the next sublayer's input u = sum_t in[t] x_t is formed and normed,
+//                        out = u / sqrt(mean(u^2) + eps) * w,
+//                    in one pass over the row.  On gathered rows (the final norm) the streams are left as they are.
+//   short_conv       c_t = sum_j taps[:, j] u_(t - T + 1 + j) on every channel of a fused projection, the T - 1
+//                    projected values before a portion's first token taken from the request's state (zeros at a
+//                    sequence's start); short_conv_keep leaves the last T - 1 projected values there.
+//   gated_scan       per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q = silu(.) and
+//                    f = lower + (1 - lower) sigmoid(. + bias), token by token with the state slice on chip; for long
+//                    portions in three launches over runs of tokens (every run from a zero state and its decay, the
+//                    runs' states carried in order, every run again from the state it starts from).
+//   head_rms         every head of a row over its root mean square, times one weight of the head's size.
+//
+// Sums, norms, gates, decays and states are float32; a result is rounded once, when it is stored in the activation type.
+#include "common.cuh"
+
+namespace streams {
+
+constexpr int MAX_STREAMS = 8;
+constexpr int MAX_TERMS = 4;
+
+struct Term {
+  const float* data;      // [partials][N][W]
+  long long stride;       // elements between partials
+  int partials;
+  float scale;
+};
+
+struct StreamNormArgs {
+  float* x;                  // [N][S][W]
+  Term terms[MAX_TERMS];
+  int num_terms;
+  const float* mix;          // [S][S], (from, to), of the pending sublayer; null: nothing is pending
+  const float* out_w;        // [S]
+  const float* layer_scale;  // [W] or null
+  const float* in_w;         // [S]; null: every stream counts once (the sum of the streams)
+  const float* norm_w;       // [W]; null: no norm, `sum_out` alone
+  float eps;
+  void* out;                 // [rows][W] in the activation type, or null
+  float* sum_out;            // [rows][W] float32 or null: u itself
+  const int* rows;           // null: every row, streams rewritten; else row r of the outputs is token rows[r]
+  int n, width, count;
+};
+
+template <typename TO, int VEC>
+__global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a) {
+  extern __shared__ float stream_shared[];   // [width] u, then 33 floats for the block's sum
+  __shared__ float mix[MAX_STREAMS * MAX_STREAMS], out_w[MAX_STREAMS], in_w[MAX_STREAMS];
+  let_dependents_start();
+  const int S = a.count;
+  const bool pending = a.mix != nullptr;
+  // parameters of the model: no kernel writes them, so they may be read before the wait
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) mix[i] = pending ? a.mix[i] : 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    out_w[i] = pending ? a.out_w[i] : 0.f;
+    in_w[i] = a.in_w != nullptr ? a.in_w[i] : 1.f;
+  }
+  wait_for_previous();
+  __syncthreads();
+  float* u_row = stream_shared;
+  float* scratch = stream_shared + a.width;
+  const int groups = a.width / VEC;
+  for (int row = blockIdx.x; row < a.n; row += gridDim.x) {
+    const int src = a.rows != nullptr ? a.rows[row] : row;
+    float* x = a.x + static_cast<size_t>(src) * S * a.width;
+    const size_t term_base = static_cast<size_t>(src) * a.width;
+    float squares = 0.f;
+    for (int group = threadIdx.x; group < groups; group += blockDim.x) {
+      const int col = group * VEC;
+      float old[MAX_STREAMS][VEC];
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s) {
+        if (s < S) {
+          if constexpr (VEC == 4) load4<float>(x + static_cast<size_t>(s) * a.width + col, old[s]);
+          else old[s][0] = x[static_cast<size_t>(s) * a.width + col];
+        }
+      }
+      float y[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) y[e] = 0.f;
+      if (pending) {
+        for (int t = 0; t < a.num_terms; ++t) {
+          const Term& term = a.terms[t];
+          float part[VEC];
+          if constexpr (VEC == 4) sum_partials4(term.data + term_base + col, term.stride, term.partials, part);
+          else part[0] = sum_partials(term.data + term_base + col, term.stride, term.partials);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y[e] = __fmaf_rn(term.scale, part[e], y[e]);
+        }
+        if (a.layer_scale != nullptr) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y[e] = __fmul_rn(y[e], a.layer_scale[col + e]);
+        }
+      }
+      float u[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) u[e] = 0.f;
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t) {
+        if (t < S) {
+          float fresh[VEC];
+          if (pending) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) fresh[e] = __fmul_rn(out_w[t], y[e]);
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+              if (s < S) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) fresh[e] = __fmaf_rn(mix[s * S + t], old[s][e], fresh[e]);
+              }
+            if (a.rows == nullptr) {
+              if constexpr (VEC == 4) store4<float>(x + static_cast<size_t>(t) * a.width + col, fresh);
+              else x[static_cast<size_t>(t) * a.width + col] = fresh[0];
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) fresh[e] = old[t][e];
+          }
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) u[e] = __fmaf_rn(in_w[t], fresh[e], u[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        u_row[col + e] = u[e];
+        squares = __fmaf_rn(u[e], u[e], squares);
+      }
+    }
+    if (a.sum_out != nullptr) {
+      __syncthreads();
+      for (int col = threadIdx.x; col < a.width; col += blockDim.x) a.sum_out[static_cast<size_t>(row) * a.width + col] = u_row[col];
+    }
+    if (a.norm_w == nullptr || a.out == nullptr) {
+      __syncthreads();
+      continue;
+    }
+    const float total = block_sum(squares, scratch);
+    const float r = rsqrtf(total / static_cast<float>(a.width) + a.eps);
+    TO* out = static_cast<TO*>(a.out) + static_cast<size_t>(row) * a.width;
+    for (int group = threadIdx.x; group < groups; group += blockDim.x) {
+      const int col = group * VEC;
+      if constexpr (VEC == 4) {
+        float w[4], v[4];
+        load4<float>(a.norm_w + col, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = u_row[col + e] * r * w[e];
+        store4<TO>(out + col, v);
+      } else {
+        out[col] = from_float<TO>(u_row[col] * r * a.norm_w[col]);
+      }
+    }
+    __syncthreads();   // the row's buffer is free for the next row
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ short_conv
+constexpr int MAX_TAPS = 32;
+
+struct ConvArgs {
+  const float* fused;     // [partials][N][total]; the first `channels` columns are convolved, the rest pass
+  long long stride;
+  int partials, total;
+  const float* bias;      // [total] or null: part of the projected value
+  const float* taps;      // [channels][T]
+  float* state;           // [slots][T - 1][channels]: the last projected values, the newest last
+  const int* q_start;     // [S + 1]
+  const int* state_slot;  // [S]; -1: no state (zeros are read, nothing is kept)
+  const int* seq_of_token;
+  float* out;             // [N][total]
+  int n, channels, taps_count, num_seqs, num_slots;
+};
+
+__device__ __forceinline__ float projected(const ConvArgs& a, int token, int c) {
+  float v = sum_partials(a.fused + static_cast<size_t>(token) * a.total + c, a.stride, a.partials);
+  if (a.bias != nullptr) v = __fadd_rn(v, a.bias[c]);
+  return v;
+}
+
+__global__ void __launch_bounds__(256) short_conv_kernel(const ConvArgs a) {
+  let_dependents_start();
+  wait_for_previous();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.total) return;
+  for (int token = blockIdx.y; token < a.n; token += gridDim.y) {
+    if (c >= a.channels) {
+      a.out[static_cast<size_t>(token) * a.total + c] = projected(a, token, c);
+      continue;
+    }
+    const int seq = a.seq_of_token[token];
+    const int index = token - a.q_start[seq];
+    const int slot = a.state_slot[seq];
+    const int T = a.taps_count;
+    const bool held = slot >= 0 && slot < a.num_slots;
+    const float* state = a.state + static_cast<size_t>(held ? slot : 0) * (T - 1) * a.channels;
+    float acc = 0.f;
+    for (int j = 0; j < T; ++j) {
+      const int lag = T - 1 - j;
+      float u;
+      if (lag <= index) u = projected(a, token - lag, c);
+      else u = held ? state[static_cast<size_t>(T - 1 - (lag - index)) * a.channels + c] : 0.f;
+      acc = __fmaf_rn(a.taps[static_cast<size_t>(c) * T + j], u, acc);
+    }
+    a.out[static_cast<size_t>(token) * a.total + c] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(256) short_conv_keep_kernel(const ConvArgs a) {
+  let_dependents_start();
+  wait_for_previous();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seq = blockIdx.y;
+  if (c >= a.channels) return;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int first = a.q_start[seq], length = a.q_start[seq + 1] - first;
+  const int keep = a.taps_count - 1;
+  float* state = a.state + static_cast<size_t>(slot) * keep * a.channels;
+  float old[MAX_TAPS];
+  for (int i = 0; i < keep; ++i) old[i] = i + length < keep ? state[static_cast<size_t>(i + length) * a.channels + c] : 0.f;
+  for (int i = 0; i < keep; ++i) {
+    const int at = length + i;   // in the old values followed by the portion's
+    state[static_cast<size_t>(i) * a.channels + c] = at < keep ? old[i] : projected(a, first + at - keep, c);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated_scan
+constexpr int SCAN_TOKENS = 8;   // tokens staged at a time
+
+struct ScanArgs {
+  const float* fused;     // [partials][N][total]: q (H D) | f (H D) | v (H Dv)
+  long long stride;
+  int partials, total;
+  const float* f_bias;    // [H D] or null
+  const float* lower;     // [H D] or null: the forget gate's lower bound
+  float* state;           // [slots][H][head_stride]: row d, column j of S at d * Dv + j
+  const int* q_start;
+  const int* state_slot;
+  float* out;             // [N][H Dv]
+  int heads, dim, vdim, head_stride, cols, row_groups, num_slots;
+  // runs of tokens (0: the whole portion is one walk from the slot's state)
+  int run;                // tokens a run holds
+  int phase;              // 1: every run from a zero state, leaves its state and its decay; 3: every run from `run_state`
+  float* run_state;       // [runs][H][D * Dv]: phase 1 writes a run's own addition, `carry` turns it into the state the run starts from
+  float* run_decay;       // [runs][H][D]: the product of a run's forget gates
+  int* run_first;         // [S + 1]: index of each sequence's first run; last, the number of runs
+  int num_seqs;
+};
+
+__device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// One CTA owns `cols` value columns of one head's state for one sequence (or one run of its tokens) and walks the
+// tokens in order.  Thread (g, j) holds rows g, g + G, ... of column j; S lives in shared memory as S[d * cols + j].
+__global__ void gated_scan_kernel(const ScanArgs a) {
+  extern __shared__ float scan_shared[];
+  let_dependents_start();
+  wait_for_previous();
+  const int D = a.dim, cols = a.cols, G = a.row_groups;
+  float* S = scan_shared;                       // [D][cols]
+  float* q = S + static_cast<size_t>(D) * cols; // [SCAN_TOKENS][D]
+  float* f = q + SCAN_TOKENS * D;               // [SCAN_TOKENS][D]
+  float* k = f + SCAN_TOKENS * D;               // [SCAN_TOKENS][D]: 1 - f
+  float* v = k + SCAN_TOKENS * D;               // [SCAN_TOKENS][cols]
+  float* red = v + SCAN_TOKENS * cols;          // [2][G][cols]
+  float* decay = red + 2 * G * cols;            // [D]: phase 1, the product of the run's gates
+  const int j = threadIdx.x % cols, g = threadIdx.x / cols;
+  const int head = blockIdx.y, col0 = blockIdx.x * cols;
+  const int cols_here = min(cols, a.vdim - col0);
+  int seq, first, length, run_index = -1;
+  if (a.run > 0) {
+    // blockIdx.z counts runs over the whole batch: find the sequence
+    run_index = blockIdx.z;
+    seq = 0;
+    while (a.run_first[seq + 1] <= run_index) ++seq;   // run_first[S] is the number of runs; blockIdx.z is below it
+    const int within = run_index - a.run_first[seq];
+    first = a.q_start[seq] + within * a.run;
+    length = min(a.run, a.q_start[seq + 1] - first);
+  } else {
+    seq = blockIdx.z;
+    first = a.q_start[seq];
+    length = a.q_start[seq + 1] - first;
+  }
+  const int slot = a.state_slot[seq];
+  const bool held = slot >= 0 && slot < a.num_slots;
+  const int HV = a.heads * a.vdim;
+  if (!held) {   // a padding row: zeros out, nothing kept
+    if (a.phase != 1)
+      for (int t = g; t < length; t += G)
+        if (j < cols_here) a.out[static_cast<size_t>(first + t) * HV + head * a.vdim + col0 + j] = 0.f;
+    return;
+  }
+  float* slot_state = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.head_stride;
+  float* run_state = a.run > 0 ? a.run_state + (static_cast<size_t>(run_index) * a.heads + head) * D * a.vdim : nullptr;
+  const float* from = a.run == 0 ? slot_state : (a.phase == 3 ? run_state : nullptr);
+  for (int d = g; d < D; d += G)
+    if (j < cols_here) S[d * cols + j] = from != nullptr ? from[static_cast<size_t>(d) * a.vdim + col0 + j] : 0.f;
+  if (a.phase == 1)
+    for (int d = threadIdx.x; d < D; d += blockDim.x) decay[d] = 1.f;
+  const int q_col = head * D, f_col = a.heads * D + head * D, v_col = 2 * a.heads * D + head * a.vdim + col0;
+  int parity = 0;
+  for (int t0 = 0; t0 < length; t0 += SCAN_TOKENS) {
+    const int here = min(SCAN_TOKENS, length - t0);
+    __syncthreads();   // the tokens staged before are used up
+    for (int i = threadIdx.x; i < here * D; i += blockDim.x) {
+      const int t = i / D, d = i - t * D;
+      const float* row = a.fused + static_cast<size_t>(first + t0 + t) * a.total;
+      const float zq = sum_partials(row + q_col + d, a.stride, a.partials);
+      float zf = sum_partials(row + f_col + d, a.stride, a.partials);
+      if (a.f_bias != nullptr) zf = __fadd_rn(zf, a.f_bias[head * D + d]);
+      const float low = a.lower != nullptr ? a.lower[head * D + d] : 0.f;
+      const float gate = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
+      q[t * D + d] = zq * sigmoid32(zq);
+      f[t * D + d] = gate;
+      k[t * D + d] = 1.0f - gate;
+    }
+    for (int i = threadIdx.x; i < here * cols; i += blockDim.x) {
+      const int t = i / cols, c = i - t * cols;
+      v[t * cols + c] = c < cols_here ? sum_partials(a.fused + static_cast<size_t>(first + t0 + t) * a.total + v_col + c, a.stride, a.partials) : 0.f;
+    }
+    __syncthreads();
+    if (a.phase == 1) {
+      // the run's own addition to the state and the product of its gates; the outputs come in phase 3
+      for (int t = 0; t < here; ++t) {
+        const float value = v[t * cols + j];
+        for (int d = g; d < D; d += G) S[d * cols + j] = __fmaf_rn(f[t * D + d], S[d * cols + j], k[t * D + d] * value);
+      }
+      if (blockIdx.x == 0)
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+          float p = decay[d];
+          for (int t = 0; t < here; ++t) p *= f[t * D + d];
+          decay[d] = p;
+        }
+      continue;
+    }
+    for (int t = 0; t < here; ++t) {
+      const float value = v[t * cols + j];
+      float partial = 0.f;
+      for (int d = g; d < D; d += G) {
+        const float s = __fmaf_rn(f[t * D + d], S[d * cols + j], k[t * D + d] * value);
+        S[d * cols + j] = s;
+        partial = __fmaf_rn(s, q[t * D + d], partial);
+      }
+      red[(parity * G + g) * cols + j] = partial;
+      __syncthreads();
+      if (g == 0 && j < cols_here) {
+        float sum = red[(parity * G) * cols + j];
+        for (int r = 1; r < G; ++r) sum = __fadd_rn(sum, red[(parity * G + r) * cols + j]);
+        a.out[static_cast<size_t>(first + t0 + t) * HV + head * a.vdim + col0 + j] = sum;
+      }
+      parity ^= 1;
+    }
+  }
+  __syncthreads();
+  if (a.phase == 1) {
+    for (int d = g; d < D; d += G)
+      if (j < cols_here) run_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[d * cols + j];
+    if (blockIdx.x == 0)
+      for (int d = threadIdx.x; d < D; d += blockDim.x) a.run_decay[(static_cast<size_t>(run_index) * a.heads + head) * D + d] = decay[d];
+    return;
+  }
+  if (a.run == 0)
+    for (int d = g; d < D; d += G)
+      if (j < cols_here) slot_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[d * cols + j];
+}
+
+// The index of every sequence's first run, from the batch's lengths: one thread, a few hundred sequences at most.
+__global__ void gated_scan_plan_kernel(const ScanArgs a) {
+  let_dependents_start();
+  wait_for_previous();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int runs = 0;
+  for (int seq = 0; seq < a.num_seqs; ++seq) {
+    a.run_first[seq] = runs;
+    runs += (a.q_start[seq + 1] - a.q_start[seq] + a.run - 1) / a.run;
+  }
+  a.run_first[a.num_seqs] = runs;
+}
+
+// The runs' states in order, elementwise: a thread per element of a head's state walks its sequence's runs; where a
+// run's own addition was, the state the run starts from is left; the state after the last run goes to the slot.
+__global__ void __launch_bounds__(256) gated_scan_carry_kernel(const ScanArgs a) {
+  let_dependents_start();
+  wait_for_previous();
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int element = blockIdx.x * blockDim.x + threadIdx.x;
+  const int size = a.dim * a.vdim;
+  if (element >= size) return;
+  const int slot = a.state_slot[seq];
+  if (slot < 0 || slot >= a.num_slots) return;
+  const int d = element / a.vdim;
+  float* slot_state = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.head_stride + element;
+  float s = *slot_state;
+  for (int run = a.run_first[seq]; run < a.run_first[seq + 1]; ++run) {
+    float* own = a.run_state + (static_cast<size_t>(run) * a.heads + head) * size + element;
+    const float added = *own;
+    const float p = a.run_decay[(static_cast<size_t>(run) * a.heads + head) * a.dim + d];
+    *own = s;
+    s = __fmaf_rn(p, s, added);
+  }
+  *slot_state = s;
+}
+
+// ------------------------------------------------------------------------------------------------ head_rms
+template <typename TO>
+__global__ void __launch_bounds__(128) head_rms_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                       TO* __restrict__ out, int n, int heads, int size, float eps) {
+  let_dependents_start();
+  wait_for_previous();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = static_cast<long long>(blockIdx.x) * 4 + warp;
+  if (unit >= static_cast<long long>(n) * heads) return;
+  const float* row = x + unit * size;
+  float squares = 0.f;
+  for (int d = lane; d < size; d += 32) squares = __fmaf_rn(row[d], row[d], squares);
+  const float r = rsqrtf(warp_sum(squares) / static_cast<float>(size) + eps);
+  for (int d = lane; d < size; d += 32) out[unit * size + d] = from_float<TO>(row[d] * r * (weight != nullptr ? weight[d] : 1.f));
+}
+
+}  // namespace streams
+
+// =========================================================================================== launchers
+using namespace streams;
+
+// terms: `num_terms` (at most 4) pending sums, term t = data[t] ([partials[t]][N][W] float32, `strides[t]` elements
+// between partials) times scales[t]; they join the streams only when `mix` is given.  out_dtype: the type of `out`.
+SHRIKE_API int shrike_stream_norm(float* x, const float* const* data, const int* partials, const long long* strides,
+                                  const float* scales, int num_terms, const float* mix, const float* out_w,
+                                  const float* layer_scale, const float* in_w, const float* norm_w, float eps, void* out,
+                                  int out_dtype, float* sum_out, const int* rows, int n, int width, int count,
+                                  cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (width < 1 || count < 1 || count > MAX_STREAMS || num_terms < 0 || num_terms > MAX_TERMS) return SHRIKE_BAD_ARGUMENT;
+  if (mix != nullptr && out_w == nullptr) return SHRIKE_BAD_ARGUMENT;
+  StreamNormArgs a = {};
+  a.x = x;
+  a.num_terms = mix != nullptr ? num_terms : 0;
+  bool vec = width % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+             reinterpret_cast<uintptr_t>(norm_w) % 16 == 0;
+  for (int t = 0; t < a.num_terms; ++t) {
+    if (data[t] == nullptr || partials[t] < 1) return SHRIKE_BAD_ARGUMENT;
+    a.terms[t] = {data[t], strides[t], partials[t], scales[t]};
+    vec = vec && reinterpret_cast<uintptr_t>(data[t]) % 16 == 0 && strides[t] % 4 == 0;
+  }
+  a.mix = mix; a.out_w = out_w; a.layer_scale = layer_scale; a.in_w = in_w; a.norm_w = norm_w; a.eps = eps;
+  a.out = out; a.sum_out = sum_out; a.rows = rows; a.n = n; a.width = width; a.count = count;
+  const size_t smem = (static_cast<size_t>(width) + 33) * sizeof(float);
+  if (smem > static_cast<size_t>(shrike_device().max_smem)) return SHRIKE_BAD_ARGUMENT;
+  const bool bf16 = out != nullptr && out_dtype == SHRIKE_BF16;
+  if (out != nullptr && out_dtype != SHRIKE_BF16 && out_dtype != SHRIKE_F32) return SHRIKE_BAD_ARGUMENT;
+  const unsigned grid = static_cast<unsigned>(n);
+#define SHRIKE_STREAM_CASE(T, V)                                                                                        \
+  do {                                                                                                                  \
+    if (smem > 48 * 1024)                                                                                               \
+      cudaFuncSetAttribute(stream_norm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    launch_dependent(stream_norm_kernel<T, V>, grid, 256, smem, stream, a);                                             \
+  } while (0)
+  if (bf16 && vec) SHRIKE_STREAM_CASE(__nv_bfloat16, 4);
+  else if (bf16) SHRIKE_STREAM_CASE(__nv_bfloat16, 1);
+  else if (vec) SHRIKE_STREAM_CASE(float, 4);
+  else SHRIKE_STREAM_CASE(float, 1);
+#undef SHRIKE_STREAM_CASE
+  return shrike_launch_status();
+}
+
+// Two launches: the convolution (every token and channel by itself), then the state (a thread a sequence and channel).
+SHRIKE_API int shrike_short_conv(const float* fused, int partials, long long stride, int total, const float* bias,
+                                 const float* taps, float* state, const int* q_start, const int* state_slot,
+                                 const int* seq_of_token, float* out, int n, int channels, int taps_count, int num_seqs,
+                                 int num_slots, cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (channels < 1 || channels > total || taps_count < 1 || taps_count > MAX_TAPS || partials < 1 || num_seqs < 1 || num_seqs > 65535)
+    return SHRIKE_BAD_ARGUMENT;
+  ConvArgs a = {fused, stride, partials, total, bias, taps, state, q_start, state_slot, seq_of_token, out,
+                n, channels, taps_count, num_seqs, num_slots};
+  const dim3 grid(static_cast<unsigned>((total + 255) / 256), static_cast<unsigned>(min(n, 65535)));
+  launch_dependent(short_conv_kernel, grid, 256, 0, stream, a);
+  if (taps_count > 1) {
+    const dim3 keep(static_cast<unsigned>((channels + 255) / 256), static_cast<unsigned>(num_seqs));
+    launch_dependent(short_conv_keep_kernel, keep, 256, 0, stream, a);
+  }
+  return shrike_launch_status();
+}
+
+// Value columns a CTA of the scan takes and the row groups its threads form, for heads of dim x vdim.
+static inline bool scan_shape(int dim, int vdim, int* cols, int* groups, size_t* smem) {
+  const size_t limit = static_cast<size_t>(shrike_device().max_smem);
+  for (int c = min(64, vdim); c >= 1; c = c > 8 ? c / 2 : c - 1) {
+    const int g = max(1, min(dim, 256 / c));
+    const size_t need = (static_cast<size_t>(dim) * c + 3 * SCAN_TOKENS * dim + SCAN_TOKENS * c + 2 * g * c + dim) * sizeof(float);
+    if (need <= limit) {
+      *cols = c; *groups = g; *smem = need;
+      return true;
+    }
+  }
+  return false;
+}
+
+SHRIKE_API long long shrike_gated_scan_runs(int n, int num_seqs, int run) { return (static_cast<long long>(n) + run - 1) / run + num_seqs; }
+
+// `run` > 0: portions are cut into runs of that many tokens, which walk side by side (three launches); `run_state`
+// (runs x heads x dim x vdim floats), `run_decay` (runs x heads x dim) and `run_first` (int32 [S + 1] of scratch: a
+// first launch leaves the index of every sequence's first run there) are then needed, and `num_runs` is the number
+// of runs the batch's lengths make, the sum of ceil(length / run).
+SHRIKE_API int shrike_gated_scan(const float* fused, int partials, long long stride, int total, const float* f_bias,
+                                 const float* lower, float* state, const int* q_start, const int* state_slot, float* out,
+                                 int num_seqs, int heads, int dim, int vdim, int head_stride, int num_slots, int run,
+                                 float* run_state, float* run_decay, int* run_first, int num_runs,
+                                 cudaStream_t stream) {
+  if (num_seqs <= 0) return SHRIKE_OK;
+  if (heads < 1 || heads > 65535 || num_seqs > 65535 || dim < 1 || vdim < 1 || partials < 1 || head_stride < dim * vdim ||
+      total < heads * (2 * dim + vdim))
+    return SHRIKE_BAD_ARGUMENT;
+  int cols = 0, groups = 0;
+  size_t smem = 0;
+  if (!scan_shape(dim, vdim, &cols, &groups, &smem)) return SHRIKE_BAD_ARGUMENT;
+  ScanArgs a = {fused, stride, partials, total, f_bias, lower, state, q_start, state_slot, out, heads, dim, vdim,
+                head_stride, cols, groups, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs};
+  if (smem > 48 * 1024) cudaFuncSetAttribute(gated_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  const unsigned slices = static_cast<unsigned>((vdim + cols - 1) / cols);
+  const unsigned threads = static_cast<unsigned>(cols * groups);
+  if (run <= 0 || run_state == nullptr || run_decay == nullptr || run_first == nullptr || num_runs < 1) {
+    launch_dependent(gated_scan_kernel, dim3(slices, heads, num_seqs), threads, smem, stream, a);
+    return shrike_launch_status();
+  }
+  if (num_runs > 65535) return SHRIKE_BAD_ARGUMENT;
+  a.run = run; a.run_state = run_state; a.run_decay = run_decay; a.run_first = run_first;
+  launch_dependent(gated_scan_plan_kernel, 1, 32, 0, stream, a);
+  a.phase = 1;
+  launch_dependent(gated_scan_kernel, dim3(slices, heads, num_runs), threads, smem, stream, a);
+  launch_dependent(gated_scan_carry_kernel, dim3((dim * vdim + 255) / 256, heads, num_seqs), 256, 0, stream, a);
+  a.phase = 3;
+  launch_dependent(gated_scan_kernel, dim3(slices, heads, num_runs), threads, smem, stream, a);
+  return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_head_rms(const float* x, const float* weight, void* out, int dtype, int n, int heads, int size,
+                               float eps, cudaStream_t stream) {
+  if (n <= 0) return SHRIKE_OK;
+  if (heads < 1 || size < 1) return SHRIKE_BAD_ARGUMENT;
+  const long long units = static_cast<long long>(n) * heads;
+  const long long blocks = (units + 3) / 4;
+  if (blocks > 0x7fffffffLL) return SHRIKE_BAD_ARGUMENT;
+  if (dtype == SHRIKE_F32)
+    launch_dependent(head_rms_kernel<float>, static_cast<unsigned>(blocks), 128, 0, stream, x, weight, static_cast<float*>(out), n, heads, size, eps);
+  else if (dtype == SHRIKE_BF16)
+    launch_dependent(head_rms_kernel<__nv_bfloat16>, static_cast<unsigned>(blocks), 128, 0, stream, x, weight,
+                     static_cast<__nv_bfloat16*>(out), n, heads, size, eps);
+  else return SHRIKE_BAD_ARGUMENT;
+  return shrike_launch_status();
+}

@@ -86,6 +86,11 @@ class DecoderModel:
             self.pass_entry = cls(spec, {local: tensors[names.pass_entry_name(local)] for local in cls.parameters(spec)},
                                   ops, runtime)
             parts.append(self.pass_entry)
+        self.residual = None
+        if config.residual is not None:
+            spec = config.residual
+            self.residual = part_class("residual", spec.kind)(spec, {}, ops, runtime)
+            parts.append(self.residual)
         norm = config.final_norm
         cls = part_class("norm", norm.kind)
         self.final_norm = cls(norm, {local: tensors[names.final_norm_name(local)] for local in cls.parameters(norm)},
@@ -114,10 +119,12 @@ class DecoderModel:
             spec = self.config.layers[run.layer].mixer
             for need in part_class("mixer", spec.kind).cache_needs(spec):
                 table = kv if isinstance(need, KVNeed) else state
-                if run.cache in table and table[run.cache] != need:
+                # a run's one state goes by the cache id, a further, named one by (cache id, name)
+                key = (run.cache, need.name) if isinstance(need, StateNeed) and need.name else run.cache
+                if key in table and table[key] != need:
                     raise ValueError(f"cache {run.cache} is used by runs with different needs")
                 if isinstance(need, (KVNeed, StateNeed)):
-                    table[run.cache] = need
+                    table[key] = need
         return kv, state
 
     def weight_bytes(self) -> int:
@@ -149,10 +156,14 @@ class DecoderModel:
         delta = None
         if self.pass_entry is not None:
             self.pass_entry.begin(resid, ctx)   # it keeps what it needs of the embedding's output
+        if self.residual is not None:
+            resid = self.residual.begin(resid, ctx)   # the residual in its own form (several streams a token)
         for run in self.config.order:
             if run.enter is not None:
                 resid, delta = self.pass_entry.forward(resid, delta, ctx, run.enter)
             resid, delta = self.blocks[run.layer].forward(resid, delta, ctx, run)
         if not ctx.num_rows:
             return self.runtime.buffer("logits", (0, self.config.vocab_size), torch.float32)
+        if self.residual is not None:
+            return self.head.forward(self.residual.finish(resid, delta, ctx.out_rows, self.final_norm))
         return self.head.forward(self.final_norm.gather_norm(resid, delta, ctx.out_rows))

@@ -76,7 +76,7 @@ class ModelRunner:
             # requests can ever hold for a group with a window
             portion = max_portion or config.max_position_embeddings
             num_pages = [num_pages if g.span is None else
-                         min(num_pages, max_slots * pages_in_flight(1 << 40, g.span, portion, page_size))
+                         min(num_pages, max_slots * pages_in_flight(1 << 40, g.span, portion, page_size, g.keep_first))
                          for g in self.groups]
         if any(count < 1 for count in num_pages):
             raise ValueError("no room for a single cache page; lower the model size or raise gpu_mem_util")

@@ -1,3 +1,3 @@
 """Architectures this engine serves.  Importing the package registers them."""
 
-from . import kavedra, qwen2, sadodra, vupitar  # noqa: F401
+from . import kavedra, qwen2, sadodra, setotar, vupitar  # noqa: F401

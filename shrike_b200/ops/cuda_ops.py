@@ -57,6 +57,9 @@ _LIMITS = {
     "tanh_norm": "at most four pending sums and two norms",
     "head_prep": "heads of at most 8192 elements, rotated dimensions even and at most the head's, the row at least as wide as q, k, v and gates",
     "matrix_memory_scan": "a positive gate cap, at most 65535 sequences and heads, the row at least as wide as q, k, v, gate and both gate columns, the state's heads at least dim * vdim + dim + 1 floats",
+    "stream_norm": "1 to 8 streams, at most four pending sums, a row that fits an SM's shared memory",
+    "short_conv": "1 to 32 taps, at most 65535 sequences, the convolved channels the projection's first columns",
+    "gated_scan": "at most 65535 sequences, heads and runs of tokens, the row at least as wide as q, f and v, the state's heads at least dim * vdim floats",
     "route_top": "at most 1024 experts, 1 <= top <= experts, the weights [N, experts] or [N, experts + 1]",
     "act_mul_blocks": "experts * each columns at most, the rest the shared expert's, which needs the weights' last column",
     "paged_attention_bf16": "at most 65535 sequences and heads, heads a multiple of kv heads, at most 32 splits",
@@ -119,6 +122,7 @@ class CudaOps:
         self._portion_tiles = None
         self._memory_scratch = None   # what the matrix memory's chunk kernels hand from one launch to the next
         self._decay_scratch = None    # the same for the decayed linear attention: a state per run of tokens
+        self._scan_scratch = None     # the gated recurrence's runs of tokens: each run's state, decay and first index
         self.portion_splits = 0  # 0: the kernel library's rule; n: that many key splits for portions (tests)
         self.generation = 0      # grows when the scratch moves
         self._held_stream = None
@@ -163,7 +167,18 @@ class CudaOps:
         lib.shrike_norm_gate.argtypes = [_P, _P, _I, _LL, _I, _I, _P, _F, _P, _I, _I, _I, _P]
         lib.shrike_latent_rope_store.argtypes = [_P, _I, _LL, _I, _P, _F, _P, _P, _F, _P, _P, _P] + [_I] * 6 + [_LL, _P]
         lib.shrike_concat_cast.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P]
-        for name in ("shrike_decay_scan", "shrike_norm_gate", "shrike_latent_rope_store", "shrike_concat_cast"):
+        lib.shrike_stream_norm.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _P]
+        lib.shrike_short_conv.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P, _P] + [_I] * 5 + [_P]
+        lib.shrike_gated_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 7 + [_P, _P, _P, _I, _P]
+        lib.shrike_gated_scan_runs.argtypes = [_I, _I, _I]
+        lib.shrike_gated_scan_runs.restype = _LL
+        lib.shrike_head_rms.argtypes = [_P, _P, _P, _I, _I, _I, _I, _F, _P]
+        lib.shrike_head_prep_norms.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P] + [_I] * 10 + [_P]
+        lib.shrike_route_top_scores.argtypes = [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P]
+        lib.shrike_act_mul_blocks_at.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P]
+        for name in ("shrike_decay_scan", "shrike_norm_gate", "shrike_latent_rope_store", "shrike_concat_cast",
+                     "shrike_stream_norm", "shrike_short_conv", "shrike_gated_scan", "shrike_head_rms",
+                     "shrike_head_prep_norms", "shrike_route_top_scores", "shrike_act_mul_blocks_at"):
             getattr(lib, name).restype = _I
         for name in ("shrike_embed_scaled", "shrike_act_mul_limit", "shrike_tanh_norm", "shrike_head_prep",
                      "shrike_matrix_memory_scan", "shrike_matrix_memory_out", "shrike_route_top", "shrike_act_mul_blocks"):
@@ -188,6 +203,10 @@ class CudaOps:
                 [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _P, _P]
             )
             lib.shrike_paged_attention_generic_sinks.restype = _I
+            lib.shrike_paged_attention_generic_kept.argtypes = (
+                [_P, _P, _P, _P, _I, _P, _P, _P] + [_I] * 6 + [_F, _I, _F, _P, _P, _I, _P, _P]
+            )
+            lib.shrike_paged_attention_generic_kept.restype = _I
             if head_dim <= build.TENSOR_CORE_HEAD_DIM:
                 self._declare_tensor_core_attention(lib)
             self._attention[head_dim] = lib
@@ -510,7 +529,7 @@ class CudaOps:
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
                         max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None,
-                        sinks=None):
+                        sinks=None, keep_first=0):
         """Attention of the batch's new tokens over the paged cache.  `window`: a query sees the `window`
         latest keys.  `chunk` (instead of a window): a query at position p sees key j <= p only when
         floor(p / chunk) = floor(j / chunk).  `max_q_len` and
@@ -519,7 +538,8 @@ class CudaOps:
         `softcap` (a positive number) and `slopes` (float32 [num_heads]) change a score
         s = scale * q.k, in this order: s <- softcap * tanh(s / softcap), then
         s <- s - slopes[head] * (query position - key position).  `sinks` (float32 [num_heads]): exp(sinks[head])
-        is one more term of every softmax's denominator: a weight that goes to nothing (the raw number, without `scale`)."""
+        is one more term of every softmax's denominator: a weight that goes to nothing (the raw number, without `scale`).
+        `keep_first` (with a window): the sequence's first `keep_first` keys stay visible to every later query."""
         _dense(q, self.dtype, "q")
         if sinks is not None:
             _dense(sinks, torch.float32, "softmax sinks")
@@ -537,13 +557,14 @@ class CudaOps:
             if window:
                 raise KernelError("attention takes a window or a chunk, not both")
             window = -int(chunk)   # the kernels' one number: > 0 a window, < 0 runs of that many positions
-        if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM:
+        keep_first = int(keep_first) if window and window > 0 else 0
+        if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM or keep_first:
             self.launches += 1
-            _check(lib.shrike_paged_attention_generic_sinks(
+            _check(lib.shrike_paged_attention_generic_kept(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),
                 _ptr(ctx_len), _ptr(seq_of_token), self.code, q.shape[0], num_heads, num_kv_heads,
-                page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(sinks), _ptr(out), self._stream()),
-                "paged_attention")
+                page_size, num_pages, scale, window or 0, softcap or 0.0, _ptr(slopes), _ptr(sinks), keep_first, _ptr(out),
+                self._stream()), "paged_attention")
             return
         if slopes is not None:
             _dense(slopes, torch.float32, "distance slopes")
@@ -734,13 +755,16 @@ class CudaOps:
                "tanh_norm")
 
     def head_prep(self, fused, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys, values, slots,
-                  gate_out, num_heads, num_kv_heads, dim, vdim, padded):
+                  gate_out, num_heads, num_kv_heads, dim, vdim, padded, whole_norm=False, value_norm=False):
         """A fused q|k|v(|gate) projection ([N, total] float32 or a K-split stack) made ready for paged
         attention: `bias` ([total] or None) added; q and k divided by their root mean square per head and
         scaled by `q_weight` / `k_weight` ([dim], None: left as they are); the first `rot` dimensions of
         every q and k head rotated, dimension i with i + rot/2, by position * inv_freq[i]; q to `q_out`
         [N, H * padded], k and v into their pages, heads `padded` elements apart (padding zeroed); with
-        `gate_out` (float32 [N, H]) the sigmoid of the last H columns."""
+        `gate_out` (float32 [N, H]) the sigmoid of the last H columns.  `whole_norm`: q and k are divided by the
+        root mean square of their whole projections instead (all heads at once), `q_weight` [H dim] and `k_weight`
+        [G dim] one number a column.  `value_norm`: every value head over its own root mean square.  `num_kv_heads`
+        0: the projection holds queries alone."""
         _dense(fused, torch.float32, "fused projection")
         _dense(q_out, self.dtype, "q")
         partials, stride = self._stack(fused)
@@ -750,10 +774,11 @@ class CudaOps:
             _dense(values, self.dtype, "value cache")
             num_slots = keys.shape[0] * keys.shape[1]
         self.launches += 1
-        _check(self.core.shrike_head_prep(
+        _check(self.core.shrike_head_prep_norms(
             _ptr(fused), partials, stride, fused.shape[-1], _ptr(bias), _ptr(positions), _ptr(inv_freq), rot if inv_freq is not None else 0,
             _ptr(q_weight), _ptr(k_weight), eps, _ptr(q_out), _ptr(keys), _ptr(values), _ptr(slots), _ptr(gate_out),
-            self.code, fused.shape[-2], num_heads, num_kv_heads, dim, vdim, padded, num_slots, self._stream()), "head_prep")
+            self.code, fused.shape[-2], num_heads, num_kv_heads, dim, vdim, padded, num_slots, int(bool(whole_norm)),
+            int(bool(value_norm)), self._stream()), "head_prep")
 
     def matrix_memory(self, fused, gate_bias, state, q_start, state_slot, numerator, denominator, weight, eps, out,
                       num_seqs, num_heads, dim, vdim, cap, floor, longest=0):
@@ -904,29 +929,126 @@ class CudaOps:
         else:
             torch.bmm(a, w.transpose(1, 2), out_dtype=torch.float32, out=target)
 
-    def route_top(self, x, router, shared_gate, weights, top, renorm_eps):
+    def route_top(self, x, router, shared_gate, weights, top, renorm_eps, scoring="softmax", renormalise=True):
         """weights [N, E (+ 1)] float32: softmax(router x) over all E experts in 32-bit, the `top` largest
         divided by their sum (+ renorm_eps), 0 elsewhere; a last column, when there is one, holds
-        sigmoid(shared_gate . x) (1 when `shared_gate` is None)."""
+        sigmoid(shared_gate . x) (1 when `shared_gate` is None).  `scoring` "sigmoid": an expert's score is the
+        sigmoid of its own logit; `renormalise` False: the chosen keep their scores as they are."""
         _dense(x, self.dtype, "router input")
         _dense(router, torch.float32, "router weight")
         _dense(weights, torch.float32, "expert weights")
         self.launches += 1
-        _check(self.core.shrike_route_top(_ptr(x), self.code, _ptr(router), _ptr(shared_gate), _ptr(weights), x.shape[0], x.shape[1],
-                                          router.shape[0], top, weights.shape[1], renorm_eps, self._stream()), "route_top")
+        _check(self.core.shrike_route_top_scores(_ptr(x), self.code, _ptr(router), _ptr(shared_gate), _ptr(weights), x.shape[0],
+                                                 x.shape[1], router.shape[0], top, weights.shape[1], renorm_eps,
+                                                 int(scoring == "sigmoid"), int(bool(renormalise)), self._stream()), "route_top")
 
-    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None):
+    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None, weight_on="output"):
         """out[n, c] = act(gate[n, c]) * up[n, c] * weights[n, e(c)] for gate_up [N, 2 I] (gate columns, then up
         columns): column c belongs to expert c // each while c < experts * each, else to the shared expert
-        (the last column of `weights`)."""
+        (the last column of `weights`).  `weight_on` "input": the weight w multiplies the expert's input, which
+        reaches gate and up alike, out = act(w gate) * (w up)."""
         _dense(gate_up, self.dtype, "gate_up")
         _dense(out, self.dtype, "activation")
         _dense(weights, torch.float32, "expert weights")
         n, inter = out.shape
         self.launches += 1
-        _check(self.core.shrike_act_mul_blocks(_ptr(gate_up), _ptr(weights), _ptr(out), self.code, n, inter, experts, each,
-                                               weights.shape[1], self.ACTIVATIONS[activation], self._limit(activation, limit),
-                                               self._stream()), "act_mul_blocks")
+        _check(self.core.shrike_act_mul_blocks_at(_ptr(gate_up), _ptr(weights), _ptr(out), self.code, n, inter, experts, each,
+                                                  weights.shape[1], self.ACTIVATIONS[activation], self._limit(activation, limit),
+                                                  int(weight_on == "input"), self._stream()), "act_mul_blocks")
+
+    # ---- several residual streams, a short convolution, a gated recurrence -----------------------------
+    def stream_norm(self, streams, pending, join, in_weights, norm_weight, eps, out, rows=None, sum_out=None):
+        """`streams` float32 [N, S, W].  `pending` (a list of (tensor, scale), each tensor float32 [N, W] or a K-split
+        stack) with `join` = (mix [S, S] indexed (from, to), out [S], layer scale [W] or None): the sublayer result
+        y = layer scale * sum of the pending terms joins the streams, x_t <- sum_s mix[s, t] x_s + out[t] y (`join`
+        None: nothing is pending).  Then u = sum_t in_weights[t] x_t (`in_weights` None: the plain sum) and
+        out = u / sqrt(mean(u^2) + eps) * norm_weight.  With `rows` (int32 [R]) only those tokens are read, the
+        streams stay as they are and out is [R, W].  `sum_out` (float32, the shape of out) receives u itself."""
+        _dense(streams, torch.float32, "residual streams")
+        n, count, width = streams.shape
+        terms = list(pending or []) if join is not None else []
+        if len(terms) > 4:
+            raise KernelError("stream_norm takes at most four pending sums")
+        data, partials, strides, scales = (_P * 4)(), (_I * 4)(), (_LL * 4)(), (_F * 4)()
+        for index, (tensor, scale) in enumerate(terms):
+            _dense(tensor, torch.float32, "pending sum")
+            if tuple(tensor.shape[-2:]) != (n, width):
+                raise KernelError(f"pending sum {tuple(tensor.shape)} does not fit {n} rows of {width}")
+            data[index] = tensor.data_ptr()
+            partials[index], strides[index] = self._stack(tensor)
+            scales[index] = float(scale)
+        mix, out_w, layer_scale = join if join is not None else (None, None, None)
+        for name, tensor in (("mix", mix), ("out", out_w), ("layer scale", layer_scale), ("in", in_weights), ("norm weight", norm_weight)):
+            if tensor is not None:
+                _dense(tensor, torch.float32, name)
+        count_rows = rows.shape[0] if rows is not None else n
+        if rows is not None:
+            _dense(rows, torch.int32, "rows")
+        for tensor in (out, sum_out):
+            if tensor is not None and (tuple(tensor.shape) != (count_rows, width) or not tensor.is_contiguous()):
+                raise KernelError(f"stream_norm output {tuple(tensor.shape)} does not fit {count_rows} rows of {width}")
+        self.launches += 1
+        _check(self.core.shrike_stream_norm(
+            _ptr(streams), data, partials, strides, scales, len(terms), _ptr(mix), _ptr(out_w), _ptr(layer_scale),
+            _ptr(in_weights), _ptr(norm_weight), eps, _ptr(out), -1 if out is None else _DTYPE_CODE[out.dtype], _ptr(sum_out),
+            _ptr(rows), count_rows, width, count, self._stream()), "stream_norm")
+
+    def short_conv(self, fused, bias, taps, state, q_start, state_slot, seq_of_token, out, num_seqs, channels):
+        """out[t, c] = sum_j taps[c, j] u[t - T + 1 + j, c] for the first `channels` columns of the projection
+        u = `fused` (+ `bias`) ([N, total] float32 or a K-split stack), the other columns copied; the T - 1 values
+        before a portion's first token come from `state` float32 [slots, T - 1, channels] (zeros when the request
+        was just opened), which is left holding the portion's last T - 1 projected values."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(taps, torch.float32, "convolution taps")
+        _dense(out, torch.float32, "convolved projection")
+        _dense(state, torch.float32, "convolution state")
+        partials, stride = self._stack(fused)
+        n, total = fused.shape[-2], fused.shape[-1]
+        if tuple(taps.shape)[0] != channels or tuple(state.shape[1:]) != (taps.shape[1] - 1, channels) or tuple(out.shape) != (n, total):
+            raise KernelError("short_conv: taps [channels, T], state [slots, T - 1, channels], out [N, total]")
+        self.launches += 2 if taps.shape[1] > 1 else 1
+        _check(self.core.shrike_short_conv(_ptr(fused), partials, stride, total, _ptr(bias), _ptr(taps), _ptr(state), _ptr(q_start),
+                                           _ptr(state_slot), _ptr(seq_of_token), _ptr(out), n, channels, taps.shape[1], num_seqs,
+                                           state.shape[0], self._stream()), "short_conv")
+
+    GATED_SCAN_RUN = 64       # tokens of a run when a portion is cut into runs that walk side by side
+    GATED_SCAN_RUNS_FROM = 192   # the longest portion of a batch from which on that is done
+
+    def gated_scan(self, fused, f_bias, lower, state, q_start, state_slot, out, num_seqs, num_heads, dim, vdim, q_lens=None):
+        """The gated linear recurrence over the batch's new tokens: per head S <- diag(f) S + (1 - f) v^T, o = S^T q,
+        with q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias) and v the columns q (H dim) | f (H dim) | v (H vdim)
+        of `fused` ([N, total] float32 or a K-split stack).  `state` float32 [slots, H, at least dim * vdim] is read
+        and left updated for the slots `state_slot` names (-1: zeros out, nothing kept); `out` float32 [N, H * vdim].
+        `q_lens` (the batch's lengths, host): long portions are cut into runs of tokens that walk side by side."""
+        _dense(fused, torch.float32, "fused projection")
+        _dense(state, torch.float32, "recurrence state")
+        _dense(out, torch.float32, "recurrence output")
+        partials, stride = self._stack(fused)
+        run, runs, run_state, run_decay, run_first = 0, 0, None, None, None
+        if q_lens is not None and max(q_lens) >= self.GATED_SCAN_RUNS_FROM:
+            run = self.GATED_SCAN_RUN
+            runs = sum(-(-length // run) for length in q_lens)
+            need = runs * num_heads * (dim * vdim + dim) + num_seqs + 1
+            if self._scan_scratch is None or self._scan_scratch.numel() < need:
+                self._scan_scratch = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=self.device)
+                self.generation += 1
+            scratch = self._scan_scratch
+            run_state = scratch[: runs * num_heads * dim * vdim]
+            run_decay = scratch[runs * num_heads * dim * vdim: runs * num_heads * (dim * vdim + dim)]
+            run_first = scratch[runs * num_heads * (dim * vdim + dim): need].view(torch.int32)
+        self.launches += 4 if run else 1
+        _check(self.core.shrike_gated_scan(
+            _ptr(fused), partials, stride, fused.shape[-1], _ptr(f_bias), _ptr(lower), _ptr(state), _ptr(q_start), _ptr(state_slot),
+            _ptr(out), num_seqs, num_heads, dim, vdim, state.shape[-1], state.shape[0], run, _ptr(run_state), _ptr(run_decay),
+            _ptr(run_first), runs, self._stream()), "gated_scan")
+
+    def head_rms(self, x, weight, eps, out, heads):
+        """out[n, h, :] = x[n, h, :] / sqrt(mean(x[n, h, :]^2) + eps) * weight for x float32 [N, heads * size]."""
+        _dense(x, torch.float32, "head outputs")
+        n, width = x.shape
+        self.launches += 1
+        _check(self.core.shrike_head_rms(_ptr(x), _ptr(weight), _ptr(out), _DTYPE_CODE[out.dtype], n, heads, width // heads, eps,
+                                         self._stream()), "head_rms")
 
     def sample(self, logits, temperature, top_p, seeds, out):
         _dense(logits, torch.float32, "logits")

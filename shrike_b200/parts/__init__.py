@@ -1,6 +1,9 @@
 """Parts a layer is put together from.  Importing the package registers the built-in ones."""
 
-from . import attention, block, embedding, experts, latent_attention, linear_attention, matrix_memory, mlp, norm, parallel, rotary  # noqa: F401
+from . import (  # noqa: F401
+    attention, block, embedding, experts, gated_recurrence, latent_attention, linear_attention, matrix_memory, mlp, norm,
+    parallel, rotary, streams,
+)
 from .base import (  # noqa: F401
     BLOCKS,
     EMBEDDINGS,

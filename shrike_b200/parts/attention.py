@@ -16,16 +16,19 @@ a query temperature that grows with the logarithm of the position, scores soft-c
 by distance, a key window.  Each of these is a parameter of its spec.
 
 `GatedHeadAttention` adds, each as an option of its spec: a norm of q and k per head, a rotation of
-part of each head (in either pairing, with stretched frequencies), chunks of positions in place of a
-window, keys and values of different sizes, a sigmoid gate per head on the output, and a learned
-sink per head in the softmax's denominator.
+part of each head (in either pairing, with stretched or divided frequencies), chunks of positions in
+place of a window, keys and values of different sizes, a sigmoid gate per head on the output, a learned
+sink per head in the softmax's denominator, a norm of q and k over the whole projection, a short causal
+convolution over time behind the projections (its last inputs are per-request state), a unit norm of every
+value head, a soft cap on the scores, a window that keeps the sequence's first keys visible, and keys and
+values read from another layer's cache.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .base import KVNeed, ParamSpec, part_class, register_part
+from .base import KVNeed, ParamSpec, StateNeed, part_class, register_part
 from .rotary import PairRotation
 
 
@@ -200,23 +203,34 @@ class GatedHeadAttention:
     capture_safe = True
 
     @staticmethod
+    def _own_kv(spec) -> bool:
+        return getattr(spec, "own_kv", True)
+
+    @staticmethod
     def parameters(spec) -> dict[str, ParamSpec]:
         q_out, k_out, v_out = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.num_kv_heads * spec.value_dim
-        params = {
-            "q_proj.weight": ParamSpec((q_out, spec.width), "matrix"),
-            "k_proj.weight": ParamSpec((k_out, spec.width), "matrix"),
-            "v_proj.weight": ParamSpec((v_out, spec.width), "matrix"),
-            "o_proj.weight": ParamSpec((spec.width, spec.num_heads * spec.value_dim), "matrix"),
-        }
+        own = GatedHeadAttention._own_kv(spec)
+        whole = spec.qk_norm == "whole"
+        params = {"q_proj.weight": ParamSpec((q_out, spec.width), "matrix")}
+        if own:
+            params["k_proj.weight"] = ParamSpec((k_out, spec.width), "matrix")
+            params["v_proj.weight"] = ParamSpec((v_out, spec.width), "matrix")
+        params["o_proj.weight"] = ParamSpec((spec.width, spec.num_heads * spec.value_dim), "matrix")
         if spec.qkv_bias:
             params["q_proj.bias"] = ParamSpec((q_out,), "bias")
-            params["k_proj.bias"] = ParamSpec((k_out,), "bias")
-            params["v_proj.bias"] = ParamSpec((v_out,), "bias")
+            if own:
+                params["k_proj.bias"] = ParamSpec((k_out,), "bias")
+                params["v_proj.bias"] = ParamSpec((v_out,), "bias")
         if spec.out_bias:
             params["o_proj.bias"] = ParamSpec((spec.width,), "bias")
         if spec.qk_norm:
-            params["q_norm.weight"] = ParamSpec((spec.head_dim,), "norm")
-            params["k_norm.weight"] = ParamSpec((spec.head_dim,), "norm")
+            params["q_norm.weight"] = ParamSpec((q_out if whole else spec.head_dim,), "norm")
+            if own:
+                params["k_norm.weight"] = ParamSpec((k_out if whole else spec.head_dim,), "norm")
+        if getattr(spec, "conv", None):
+            params["q_conv.weight"] = ParamSpec((q_out, spec.conv), "conv")
+            params["k_conv.weight"] = ParamSpec((k_out, spec.conv), "conv")
+            params["v_conv.weight"] = ParamSpec((v_out, spec.conv), "conv")
         if spec.head_gate:
             params["gate.weight"] = ParamSpec((spec.num_heads, spec.width), "matrix")
         if getattr(spec, "sink", False):
@@ -225,23 +239,37 @@ class GatedHeadAttention:
 
     @staticmethod
     def cache_needs(spec) -> list:
-        return [KVNeed(spec.num_kv_heads, padded_head(max(spec.head_dim, spec.value_dim)), spec.window, chunk=spec.chunk)]
+        needs = [KVNeed(spec.num_kv_heads, padded_head(max(spec.head_dim, spec.value_dim)), spec.window, chunk=spec.chunk,
+                        keep_first=getattr(spec, "keep_first", 0) if spec.window is not None else 0)]
+        taps = getattr(spec, "conv", None)
+        if taps and taps > 1:   # the last projected q, k and v of the request, the newest last
+            channels = spec.num_heads * spec.head_dim + spec.num_kv_heads * (spec.head_dim + spec.value_dim)
+            needs.append(StateNeed((taps - 1, channels), "float32", name="conv"))
+        return needs
 
     def __init__(self, spec, tensors, ops, runtime):
         self.spec, self.ops, self.runtime = spec, ops, runtime
         self.padded = padded_head(max(spec.head_dim, spec.value_dim))
         ops.check_head_dim(self.padded)
+        self.own_kv = self._own_kv(spec)
+        self.whole_norm = spec.qk_norm == "whole"
+        projections = (("q_proj", spec.num_heads), ("k_proj", spec.num_kv_heads)) if self.own_kv else (("q_proj", spec.num_heads),)
         rotation = None
         if getattr(spec, "rotation", None) is not None:
             # the kernel pairs dimension i with i + dims/2: another pairing, and a factor on cos and sin,
             # become a reordering and a scaling of the q and k rows (weights and biases alike)
             rotation = PairRotation(spec.rotation, runtime.device)
-            for name, heads in (("q_proj", spec.num_heads), ("k_proj", spec.num_kv_heads)):
-                for kind in ("weight", "bias") if spec.qkv_bias else ("weight",):
-                    tensors[f"{name}.{kind}"] = rotation.arrange_rows(tensors[f"{name}.{kind}"], heads, spec.head_dim)
-            if spec.qk_norm and rotation.order != list(range(spec.rotation.dims)):
-                raise NotImplementedError("a per-head norm weight with neighbours paired: the weight is not reordered")
-        rows = [tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight"), tensors.pop("v_proj.weight")]
+            reordered = rotation.order != list(range(spec.rotation.dims))
+            if (spec.qk_norm or getattr(spec, "conv", None)) and reordered:
+                raise NotImplementedError("a q/k norm weight or a convolution with neighbours paired: those are not reordered")
+            if not spec.qk_norm:   # with a norm between projection and rotation the factor goes into the norm's weight
+                for name, heads in projections:
+                    for kind in ("weight", "bias") if spec.qkv_bias else ("weight",):
+                        tensors[f"{name}.{kind}"] = rotation.arrange_rows(tensors[f"{name}.{kind}"], heads, spec.head_dim)
+        rows = [tensors.pop("q_proj.weight")]
+        if self.own_kv:
+            rows += [tensors.pop("k_proj.weight"), tensors.pop("v_proj.weight")]
+        self.channels = sum(r.shape[0] for r in rows)   # what a convolution runs over: q, k and v
         if spec.head_gate:
             rows.append(tensors.pop("gate.weight").to(rows[0].dtype))
         extra = -sum(r.shape[0] for r in rows) % 16   # rows of zeros: output rows of a whole number of 64 bytes
@@ -252,9 +280,13 @@ class GatedHeadAttention:
         self.bias = None
         if spec.qkv_bias:
             bias = torch.zeros(self.total, dtype=torch.float32, device=self.w_fused.device)   # the gate has none
-            given = torch.cat([tensors.pop("q_proj.bias"), tensors.pop("k_proj.bias"), tensors.pop("v_proj.bias")])
+            given = [tensors.pop("q_proj.bias")] + ([tensors.pop("k_proj.bias"), tensors.pop("v_proj.bias")] if self.own_kv else [])
+            given = torch.cat(given)
             bias[: given.numel()] = given.to(torch.float32)
             self.bias = bias
+        self.taps = None
+        if getattr(spec, "conv", None):
+            self.taps = torch.cat([tensors.pop(f"{name}_conv.weight") for name in ("q", "k", "v")]).to(torch.float32).contiguous()
         w_o = tensors.pop("o_proj.weight")
         if self.padded != spec.value_dim:   # the kernels' heads are wider: the added columns meet zeros
             wide = w_o.new_zeros(spec.width, spec.num_heads, self.padded)
@@ -265,7 +297,16 @@ class GatedHeadAttention:
         self.q_weight = self.k_weight = None
         if spec.qk_norm:
             self.q_weight = tensors.pop("q_norm.weight").to(torch.float32).contiguous()
-            self.k_weight = tensors.pop("k_norm.weight").to(torch.float32).contiguous()
+            self.k_weight = tensors.pop("k_norm.weight").to(torch.float32).contiguous() if self.own_kv else None
+            if rotation is not None and rotation.gain != 1.0:
+                # the factor on cos and sin: a rotation is linear, so the rotated dimensions' norm weights carry it
+                def with_gain(weight, heads):
+                    shaped = weight.view(heads if self.whole_norm else 1, spec.head_dim).clone()
+                    shaped[:, : spec.rotation.dims] *= rotation.gain
+                    return shaped.reshape(-1).contiguous()
+                self.q_weight = with_gain(self.q_weight, spec.num_heads)
+                if self.k_weight is not None:
+                    self.k_weight = with_gain(self.k_weight, spec.num_kv_heads)
         self.inv_freq, self.rot = None, 0
         if spec.rotary is not None:
             dims, base = spec.rotary
@@ -278,17 +319,29 @@ class GatedHeadAttention:
 
     def forward(self, x, ctx, run):
         spec, rt, ops = self.spec, self.runtime, self.ops
+        if run.writes_cache != self.own_kv:
+            raise ValueError("a layer with key and value projections writes its cache; one without reads another's")
         n = x.shape[0]
         fused = rt.buffer("qkv", (n, self.total), torch.float32)
         fused = ops.linear(x, self.w_fused, fused, allow_partials=True)
+        bias = self.bias
+        if self.taps is not None:
+            # the convolution over time runs on the projected values, bias included; the T - 1 before this portion
+            # are the request's state
+            mixed = rt.buffer("qkv_conv", (n, self.total), torch.float32)
+            ops.short_conv(fused, bias, self.taps, ctx.storage.state[(run.cache, "conv")] if self.taps.shape[1] > 1 else self._no_state(),
+                           ctx.q_start, ctx.state_slot, ctx.seq_of_token, mixed, ctx.num_seqs, self.channels)
+            fused, bias = mixed, None
         group, keys, values = ctx.storage.keys_values(run.cache)
         view = ctx.groups[group]
         q = rt.buffer("q", (n, self.out_width), rt.act_dtype)
         gate = rt.buffer("head_gate", (n, spec.num_heads), torch.float32) if spec.head_gate else None
         ops.head_prep(
-            fused, self.bias, ctx.positions, self.inv_freq, self.rot, self.q_weight, self.k_weight, spec.eps, q,
+            fused, bias, ctx.positions, self.inv_freq, self.rot, self.q_weight, self.k_weight, spec.eps, q,
             keys if run.writes_cache else None, values if run.writes_cache else None, view.slot_mapping, gate,
-            spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim, self.padded,
+            spec.num_heads, spec.num_kv_heads if self.own_kv else 0, spec.head_dim, spec.value_dim, self.padded,
+            **({"whole_norm": True} if self.whole_norm else {}),
+            **({"value_norm": True} if getattr(spec, "value_norm", False) else {}),
         )
         attn = rt.buffer("attn_out", (n, self.out_width), rt.act_dtype)
         ops.paged_attention(
@@ -297,11 +350,17 @@ class GatedHeadAttention:
             max_q_len=ctx.max_q_len, max_ctx_len=ctx.max_ctx_len, min_q_len=ctx.min_q_len, q_lens=ctx.q_lens,
             **({"chunk": spec.chunk} if spec.chunk is not None else {}),
             **({"sinks": self.sinks} if self.sinks is not None else {}),
+            **({"softcap": spec.softcap} if getattr(spec, "softcap", None) else {}),
+            **({"keep_first": spec.keep_first} if getattr(spec, "keep_first", 0) else {}),
         )
         if gate is not None:
             ops.head_scale(attn, gate, spec.num_heads, self.padded)
         delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
         return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)
+
+    def _no_state(self):
+        """A convolution of one tap keeps nothing: an empty state of the right shape."""
+        return torch.zeros((1, 0, self.channels), dtype=torch.float32, device=self.runtime.device)
 
 
 register_part("mixer", "attention", PagedAttention)

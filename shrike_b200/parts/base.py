@@ -42,6 +42,12 @@ be checked and the cache sized before anything is put on the device):
                                        that fills it says so with ctx.carried["embedding_copied"] = True
       begin(resid_f32, ctx)            right after the embedding: keeps what later passes need of it
       forward(resid_f32, delta, ctx, t) -> (resid_f32, delta)   what entering pass t does to the residual
+  join (a block that lists one per sublayer, roles "mixer_join" and "feed_forward_join")
+      read_norm(streams_f32[N,S*W], pending | None, norm) -> normed[N,W]
+          the pending sublayer result joins the streams, then the next sublayer's input is formed and normed
+  residual (a model whose residual is several streams a token; `ModelConfig.residual`)
+      begin(resid_f32[N,W], ctx) -> streams_f32[N,S*W]       right after the embedding
+      finish(streams, pending, rows_i32[R], norm) -> normed[R,W]   the final norm's input on the wanted rows
   head
       forward(hidden[R,W]) -> float32 logits [R, vocab]   (hidden: the final norm's output on the
           wanted rows); built with tensors {"weight": ...}, the embedding's table when tied
@@ -63,7 +69,8 @@ class ParamSpec:
     """A tensor a part expects: its shape and how random weights fill it.
 
     init: "matrix" | "table" (N(0, 0.02)), "bias" (N(0, 0.02)), "norm" (1 + N(0, 0.1)),
-    "around_zero" (N(0, 0.1)), "sink" (N(0, 1)), "mix" ([W, 2 W]: identity | 0, plus N(0, 0.02)).
+    "around_zero" (N(0, 0.1)), "sink" (N(0, 1)), "mix" ([W, 2 W]: identity | 0, plus N(0, 0.02)),
+    "conv" (N(0, 0.4)), "unit_interval" (sigmoid of N(0, 1)), "stream_mix" ([S, S]: identity plus N(0, 0.15)).
     """
 
     shape: tuple[int, ...]
@@ -82,14 +89,20 @@ class KVNeed:
     window: int | None = None
     planes: int = 2
     chunk: int | None = None
+    # with a window: a sequence's first `keep_first` keys stay visible to every later query, so the pages that hold
+    # them are never given back
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-request state of fixed size, one slot per live request."""
+    """Per-request state of fixed size, one slot per live request.  `name` "": the run's one state,
+    `storage.state[cache id]`; a mixer that needs a second state beside it (the last inputs of a short
+    convolution, say) names it, and finds it at `storage.state[(cache id, name)]`."""
 
     shape: tuple[int, ...]
     dtype: str = "float32"
+    name: str = ""
 
 
 class PendingSum:
@@ -120,11 +133,15 @@ BLOCKS: dict[str, type] = {}
 EMBEDDINGS: dict[str, type] = {}
 HEADS: dict[str, type] = {}
 PASS_ENTRIES: dict[str, type] = {}
+JOINS: dict[str, type] = {}       # how a sublayer's result joins the residual (a layer lists them as further roles)
+RESIDUALS: dict[str, type] = {}   # a residual that is not one row a token (`ModelConfig.residual`)
 
 _CATEGORIES = {
     "embedding": EMBEDDINGS,
     "head": HEADS,
     "pass_entry": PASS_ENTRIES,
+    "join": JOINS,
+    "residual": RESIDUALS,
     "mixer": MIXERS,
     "feed_forward": FEED_FORWARDS,
     "norm": NORMS,
@@ -135,7 +152,7 @@ _CATEGORIES = {
 
 def register_part(category: str, kind: str, cls: type) -> type:
     """Adds a part class; `category` is one of mixer, feed_forward, norm, position, block,
-    embedding, head, pass_entry."""
+    embedding, head, pass_entry, join, residual."""
     _CATEGORIES[category][kind] = cls
     return cls
 

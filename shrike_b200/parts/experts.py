@@ -1,4 +1,4 @@
-"""A mixture of gated feed-forward experts with a softmax router, and a shared expert beside them.
+"""A mixture of gated feed-forward experts with a softmax (or sigmoid) router, and a shared expert beside them.
 
 Router logits are formed in 32-bit; scores are the softmax over ALL experts; the `top` largest are
 chosen and their scores divided by their sum (+ a tiny constant); the output is the weighted sum of
@@ -10,7 +10,10 @@ last), so one product gives every expert's gate and up columns for every token; 
 kernel multiplies each column by its expert's weight for that token, which is exactly 0 for an
 expert the token did not choose; one product with the stacked down matrices then IS the weighted
 sum.  Nothing depends on which experts the tokens chose, so a step's launches are the same for
-every batch of a shape and can be replayed.  The price is arithmetic: every expert's columns are
+every batch of a shape and can be replayed.  Options of the spec: `scoring` "sigmoid" (an expert's score
+is the sigmoid of its own logit), `renormalise` False (the chosen keep their scores), `weight_on` "input" (an expert
+runs on weight * x: gate and up are linear in x, so the activation kernel forms act(w gate) * (w up) from the same
+product).  The price is arithmetic: every expert's columns are
 computed for every token, experts / top times what the chosen ones alone would take; in decoding,
 where the experts' weights are read once whatever the routing, it costs nothing.
 """
@@ -59,11 +62,14 @@ class RoutedExperts:
         spec, rt, ops = self.spec, self.runtime, self.ops
         n = x.shape[0]
         share = rt.buffer("expert_share", (n, self.columns), torch.float32)
-        ops.route_top(x, self.router, self.shared_gate, share, spec.top, spec.renorm_eps)
+        ops.route_top(x, self.router, self.shared_gate, share, spec.top, spec.renorm_eps,
+                      **({"scoring": spec.scoring} if getattr(spec, "scoring", "softmax") != "softmax" else {}),
+                      **({"renormalise": False} if not getattr(spec, "renormalise", True) else {}))
         gate_up = rt.buffer("experts_gate_up", (n, 2 * self.inter), rt.act_dtype)
         ops.linear(x, self.w_gate_up, gate_up)
         act = rt.buffer("experts_act", (n, self.inter), rt.act_dtype)
-        ops.act_mul_blocks(gate_up, share, act, spec.experts, spec.intermediate, spec.activation)
+        ops.act_mul_blocks(gate_up, share, act, spec.experts, spec.intermediate, spec.activation,
+                           **({"weight_on": "input"} if getattr(spec, "weight_on", "output") == "input" else {}))
         delta = rt.buffer("ffn_delta", (n, spec.width), torch.float32)
         return ops.linear(act, self.w_down, delta, allow_partials=True)
 

@@ -26,9 +26,9 @@ class ParallelMixer:
         needs = []
         for name, branch, _scale in spec.branches:
             needs += part_class("mixer", branch.kind).cache_needs(branch)
-        for sort in (KVNeed, StateNeed):
-            if sum(isinstance(need, sort) for need in needs) > 1:
-                raise ValueError("a parallel mixer holds at most one branch with pages and one with state")
+        names = [need.name for need in needs if isinstance(need, StateNeed)]
+        if sum(isinstance(need, KVNeed) for need in needs) > 1 or len(set(names)) != len(names):
+            raise ValueError("a parallel mixer holds at most one branch with pages and one state of each name")
         return needs
 
     def __init__(self, spec, tensors, ops, runtime):

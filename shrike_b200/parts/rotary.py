@@ -64,6 +64,8 @@ class PairRotation:
                 ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
                 freq[i] = freq[i] / factor * ramp + freq[i] * (1.0 - ramp)
             self.gain = 0.1 * math.log(factor) + 1.0
+        if getattr(spec, "divide", None) is not None:   # linear scaling: every frequency over one number
+            freq = [f / float(spec.divide) for f in freq]
         self.inv_freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device)
         self.order = list(range(dims))
         if spec.pairing == "neighbours":

@@ -39,6 +39,12 @@ def random_tensor(name: str, spec, seed: int, device="cpu", dtype=torch.float32)
         values = 0.1 * values
     elif spec.init == "sink":
         pass
+    elif spec.init == "conv":            # taps of a short convolution: of the order of one, so that every tap counts
+        values = 0.4 * values
+    elif spec.init == "unit_interval":   # a bound inside (0, 1)
+        values = torch.sigmoid(values)
+    elif spec.init == "stream_mix":      # [S, S]: near the identity, so that the streams stay apart
+        values = 0.15 * values + torch.eye(spec.shape[0], device=device)
     elif spec.init == "mix":   # [W, 2 W]: the identity on the first half plus noise, so that a residual stays one
         values = 0.02 * values
         values[:, : spec.shape[0]] += torch.eye(spec.shape[0], device=device)

@@ -48,7 +48,7 @@ class EmulatedOps:
             out.copy_((torch.tanh(alpha * x) * weight + bias).to(out.dtype))
 
     def head_prep(self, fused, bias, positions, inv_freq, rot, q_weight, k_weight, eps, q_out, keys, values, slots,
-                  gate_out, num_heads, num_kv_heads, dim, vdim, padded):
+                  gate_out, num_heads, num_kv_heads, dim, vdim, padded, whole_norm=False, value_norm=False):
         if fused.dim() == 3:
             fused = fused.sum(0)
         n = fused.shape[0]
@@ -57,10 +57,18 @@ class EmulatedOps:
         q = x[:, :q_cols].view(n, num_heads, dim)
         k = x[:, q_cols: q_cols + k_cols].view(n, num_kv_heads, dim)
         v = x[:, q_cols + k_cols: q_cols + k_cols + v_cols].view(n, num_kv_heads, vdim)
-        if q_weight is not None:
-            q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
-        if k_weight is not None:
-            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if whole_norm:   # over the whole projection, one weight a column
+            if q_weight is not None:
+                q = (q / torch.sqrt(q.pow(2).mean((-2, -1), keepdim=True) + eps)) * q_weight.view(num_heads, dim)
+            if k_weight is not None and num_kv_heads:
+                k = (k / torch.sqrt(k.pow(2).mean((-2, -1), keepdim=True) + eps)) * k_weight.view(num_kv_heads, dim)
+        else:
+            if q_weight is not None:
+                q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+            if k_weight is not None:
+                k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if value_norm and num_kv_heads:
+            v = v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)
         if inv_freq is not None and rot:
             half = rot // 2
             angle = positions.float()[:, None] * inv_freq[None, :]
@@ -120,19 +128,25 @@ class EmulatedOps:
             held[:, D * Dv: D * Dv + D] = z
             held[:, D * Dv + D] = m
 
-    def route_top(self, x, router, shared_gate, weights, top, renorm_eps):
-        scores = torch.softmax(x.float() @ router.T, -1)
+    def route_top(self, x, router, shared_gate, weights, top, renorm_eps, scoring="softmax", renormalise=True):
+        logits = x.float() @ router.T
+        scores = torch.sigmoid(logits) if scoring == "sigmoid" else torch.softmax(logits, -1)
         best, chosen = torch.topk(scores, top, -1)
         weights.zero_()
-        weights[:, : router.shape[0]].scatter_(1, chosen, best / (best.sum(-1, keepdim=True) + renorm_eps))
+        weights[:, : router.shape[0]].scatter_(1, chosen, best / (best.sum(-1, keepdim=True) + renorm_eps) if renormalise else best)
         if weights.shape[1] > router.shape[0]:
             weights[:, -1] = 1.0 if shared_gate is None else torch.sigmoid(x.float() @ shared_gate)
 
-    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None):
+    def act_mul_blocks(self, gate_up, weights, out, experts, each, activation="silu", limit=None, weight_on="output"):
         inter = out.shape[1]
         column = torch.arange(inter)
         block = torch.where(column < experts * each, column // each, torch.full_like(column, experts))
         plain = torch.empty(out.shape, dtype=torch.float32)
+        if weight_on == "input":   # the weight reaches gate and up alike
+            share = weights[:, block]
+            self.act_mul((gate_up.float() * torch.cat([share, share], -1)).to(gate_up.dtype), plain, 0, activation, limit)
+            out.copy_(plain.to(out.dtype))
+            return
         self.act_mul(gate_up, plain, 0, activation, limit)
         out.copy_((plain * weights[:, block]).to(out.dtype))
 
@@ -327,7 +341,7 @@ class EmulatedOps:
     def paged_attention(self, q, keys, values, block_table, q_start, ctx_len, seq_of_token,
                         num_heads, num_kv_heads, head_dim, scale, window, out,
                         max_q_len=0, max_ctx_len=0, min_q_len=0, q_lens=None, softcap=None, slopes=None, chunk=None,
-                        sinks=None):
+                        sinks=None, keep_first=0):
         page = keys.shape[1]
         group = num_heads // num_kv_heads
         n = q.shape[0]
@@ -340,6 +354,8 @@ class EmulatedOps:
             if chunk:
                 first = last // chunk * chunk
             idx = torch.arange(first, last + 1)
+            if window and keep_first:   # the sequence's first keys stay visible behind the window
+                idx = torch.cat([torch.arange(0, min(keep_first, first)), idx])
             pages = block_table[s].long()[idx // page]
             assert (pages >= 0).all(), "attention read a page that was given back"
             k = keys[pages, idx % page].float()  # [c, Hkv, D]
@@ -357,6 +373,71 @@ class EmulatedOps:
                 probs = scores.softmax(-1)
             o = torch.einsum("kgc,ckd->kgd", probs, v)
             out[token] = o.reshape(-1).to(out.dtype)
+
+    def stream_norm(self, streams, pending, join, in_weights, norm_weight, eps, out, rows=None, sum_out=None):
+        x = streams if rows is None else streams[rows.long()]
+        if join is not None:
+            mix, out_w, layer_scale = join
+            y = 0.0
+            for tensor, scale in pending or []:
+                summed = tensor.float().sum(0) if tensor.dim() == 3 else tensor.float()
+                y = y + scale * (summed if rows is None else summed[rows.long()])
+            if layer_scale is not None:
+                y = y * layer_scale
+            x = torch.einsum("st,nsw->ntw", mix, x) + out_w[None, :, None] * y[:, None, :]
+            if rows is None:
+                streams.copy_(x)
+        u = x.sum(1) if in_weights is None else torch.einsum("s,nsw->nw", in_weights, x)
+        if sum_out is not None:
+            sum_out.copy_(u)
+        if out is not None and norm_weight is not None:
+            out.copy_((u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps) * norm_weight).to(out.dtype))
+
+    def short_conv(self, fused, bias, taps, state, q_start, state_slot, seq_of_token, out, num_seqs, channels):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        u = fused.float() if bias is None else fused.float() + bias
+        out.copy_(u)
+        count = taps.shape[1]
+        for s in range(num_seqs):
+            a, b, slot = int(q_start[s]), int(q_start[s + 1]), int(state_slot[s])
+            before = state[slot] if slot >= 0 else torch.zeros(count - 1, channels)
+            joined = torch.cat([before, u[a:b, :channels]])
+            mixed = torch.zeros(b - a, channels)
+            for j in range(count):
+                mixed += joined[j: j + b - a] * taps[:, j]
+            out[a:b, :channels] = mixed
+            if slot >= 0 and count > 1:
+                state[slot] = joined[-(count - 1):]
+
+    def gated_scan(self, fused, f_bias, lower, state, q_start, state_slot, out, num_seqs, num_heads, dim, vdim, q_lens=None):
+        if fused.dim() == 3:
+            fused = fused.sum(0)
+        x = fused.float()
+        H, D, Dv = num_heads, dim, vdim
+        out.zero_()
+        for s in range(num_seqs):
+            slot = int(state_slot[s])
+            if slot < 0:
+                continue
+            S = state[slot][:, : D * Dv].reshape(H, D, Dv).clone()
+            for t in range(int(q_start[s]), int(q_start[s + 1])):
+                zq, zf = x[t, : H * D], x[t, H * D: 2 * H * D]
+                v = x[t, 2 * H * D: 2 * H * D + H * Dv].view(H, Dv)
+                gate = torch.sigmoid(zf if f_bias is None else zf + f_bias)
+                low = lower if lower is not None else torch.zeros_like(gate)
+                f = (low + (1.0 - low) * gate).view(H, D)
+                q = (zq * torch.sigmoid(zq)).view(H, D)
+                S = f[:, :, None] * S + (1.0 - f)[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+            state[slot][:, : D * Dv] = S.reshape(H, -1)
+
+    def head_rms(self, x, weight, eps, out, heads):
+        shaped = x.float().view(x.shape[0], heads, -1)
+        normed = shaped / torch.sqrt(shaped.pow(2).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            normed = normed * weight
+        out.copy_(normed.reshape(x.shape).to(out.dtype))
 
     def silu_mul(self, gate_up, out):
         self.act_mul(gate_up, out)
