@@ -314,10 +314,11 @@ __global__ void gated_scan_kernel(const ScanArgs a) {
       float zf = sum_partials(row + f_col + d, a.stride, a.partials);
       if (a.f_bias != nullptr) zf = __fadd_rn(zf, a.f_bias[head * D + d]);
       const float low = a.lower != nullptr ? a.lower[head * D + d] : 0.f;
-      const float gate = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
+      // 1 - f = (1 - lower) (1 - sigmoid(z)) = (1 - lower) sigmoid(-z): formed so, a gate close to one keeps the
+      // digits of what it lets in, which 1 - f computed from f would lose
       q[t * D + d] = zq * sigmoid32(zq);
-      f[t * D + d] = gate;
-      k[t * D + d] = 1.0f - gate;
+      f[t * D + d] = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
+      k[t * D + d] = (1.0f - low) * sigmoid32(-zf);
     }
     for (int i = threadIdx.x; i < here * cols; i += blockDim.x) {
       const int t = i / cols, c = i - t * cols;

@@ -287,6 +287,8 @@ class GatedHeadAttention:
         self.taps = None
         if getattr(spec, "conv", None):
             self.taps = torch.cat([tensors.pop(f"{name}_conv.weight") for name in ("q", "k", "v")]).to(torch.float32).contiguous()
+            # a convolution of one tap keeps nothing: an empty state of the right shape stands in
+            self.no_state = torch.zeros((1, 0, self.channels), dtype=torch.float32, device=self.taps.device)
         w_o = tensors.pop("o_proj.weight")
         if self.padded != spec.value_dim:   # the kernels' heads are wider: the added columns meet zeros
             wide = w_o.new_zeros(spec.width, spec.num_heads, self.padded)
@@ -329,7 +331,7 @@ class GatedHeadAttention:
             # the convolution over time runs on the projected values, bias included; the T - 1 before this portion
             # are the request's state
             mixed = rt.buffer("qkv_conv", (n, self.total), torch.float32)
-            ops.short_conv(fused, bias, self.taps, ctx.storage.state[(run.cache, "conv")] if self.taps.shape[1] > 1 else self._no_state(),
+            ops.short_conv(fused, bias, self.taps, ctx.storage.state[(run.cache, "conv")] if self.taps.shape[1] > 1 else self.no_state,
                            ctx.q_start, ctx.state_slot, ctx.seq_of_token, mixed, ctx.num_seqs, self.channels)
             fused, bias = mixed, None
         group, keys, values = ctx.storage.keys_values(run.cache)
@@ -357,10 +359,6 @@ class GatedHeadAttention:
             ops.head_scale(attn, gate, spec.num_heads, self.padded)
         delta = rt.buffer("mixer_delta", (n, spec.width), torch.float32)
         return ops.linear(attn, self.w_o, delta, bias=self.b_o, allow_partials=True)
-
-    def _no_state(self):
-        """A convolution of one tap keeps nothing: an empty state of the right shape."""
-        return torch.zeros((1, 0, self.channels), dtype=torch.float32, device=self.runtime.device)
 
 
 register_part("mixer", "attention", PagedAttention)

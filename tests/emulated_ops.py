@@ -401,7 +401,7 @@ class EmulatedOps:
         count = taps.shape[1]
         for s in range(num_seqs):
             a, b, slot = int(q_start[s]), int(q_start[s + 1]), int(state_slot[s])
-            before = state[slot] if slot >= 0 else torch.zeros(count - 1, channels)
+            before = state[slot] if slot >= 0 and count > 1 else torch.zeros(count - 1, channels)
             joined = torch.cat([before, u[a:b, :channels]])
             mixed = torch.zeros(b - a, channels)
             for j in range(count):
