@@ -106,7 +106,17 @@ struct Params {
   // (a sink: its share of the weight attends to nothing; taken as it is, without `scale`).  It is added where a row's
   // sum is final.
   const float* sinks;
+  // with a window (> 0): the sequence's first `keep_first` keys stay visible to every later query.  The tiles that
+  // hold them are walked first, then the window's own
+  int keep_first;
 };
+
+// Tiles a walk takes with kept first keys: the `pre` tiles that hold them and lie wholly before the window's first
+// tile, then the window's tiles from `tile_lo` on.  Tile number v of the walk is this tile of the sequence.
+__device__ __forceinline__ int tiles_before_window(int keep_first, int window, int tile_lo, int tile_keys) {
+  return window > 0 && keep_first > 0 ? min((keep_first + tile_keys - 1) / tile_keys, tile_lo) : 0;
+}
+__device__ __forceinline__ int walked_tile(int v, int pre, int tile_lo) { return v < pre ? v : tile_lo + (v - pre); }
 
 // The sink's term of a row's sum whose exponentials are taken relative to `max_log2` (scores times log2 e).
 // A row that saw no key has the maximum -inf: the term is +inf and the row's output 0, as without a sink.
@@ -134,7 +144,7 @@ __device__ __forceinline__ float modified_score(float dot, float scale, float so
 // row: the page of key j (-1: none, -2: leave the row untouched), then the row's offset.
 __device__ __forceinline__ int lookup_page(const Params& p, const int* table, int j, int lo, int hi, int leave_out) {
   if (j == leave_out) return -2;
-  if (j < lo || j > hi) return -1;
+  if ((j < lo && j >= p.keep_first) || j > hi) return -1;
   const int block = p.page_shift >= 0 ? j >> p.page_shift : j / p.page_size;
   return block < p.max_blocks ? table[block] : -1;
 }
@@ -240,7 +250,7 @@ template <int NT>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTILES][4], float (&row_max)[2],
                                                float (&row_sum)[2], const int (&first)[2], const int (&last)[2],
                                                int key_base, float scale_log2, int lane, bool modified = false,
-                                               float scale = 0.f, float softcap = 0.f, float slope = 0.f) {
+                                               float scale = 0.f, float softcap = 0.f, float slope = 0.f, int keep_first = 0) {
   float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int j = 0; j < NT; ++j)
@@ -248,7 +258,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[DTI
     for (int e = 0; e < 4; ++e) {
       const int key = key_base + j * 8 + (lane & 3) * 2 + (e & 1);
       const int r = e >> 1;
-      const bool seen = key >= first[r] && key <= last[r];
+      const bool seen = (key >= first[r] || key < keep_first) && key <= last[r];
       const float value = modified ? modified_score(s[j][e], scale, softcap, slope, last[r] - key) : s[j][e] * scale_log2;
       s[j][e] = seen ? value : -INFINITY;
       tile_max[r] = fmaxf(tile_max[r], s[j][e]);
@@ -303,6 +313,9 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   const int lo = first_visible_key(pos0 + tile_start, p.window);
   const int hi = pos0 + tile_start + rows_here - 1;
   const int tile_lo = lo / PBN, tile_hi = hi / PBN;
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int pre = tiles_before_window(keep, p.window, tile_lo, PBN);
+  const int walked = pre + tile_hi - tile_lo + 1;   // tiles of this walk: the kept keys' own, then the window's
 
   for (int c = threadIdx.x; c < BM * CHUNKS; c += THREADS) {
     const int row = c / CHUNKS, chunk = c - row * CHUNKS;
@@ -312,7 +325,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   }
   // keys that are their own values (a cached latent, one plane of pages): one tile serves both products
   const bool own_values = p.k_cache != p.v_cache;
-  load_kv_tile<PBN>(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, tile_lo * PBN, lo, hi, own_values);
+  load_kv_tile<PBN>(k_tiles, v_tiles, tile_rows[0], p, table, kv_head, walked_tile(0, pre, tile_lo) * PBN, lo, hi, own_values);
   cp_async_commit();
 
   int first[2], last[2];
@@ -333,11 +346,12 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
   unsigned q_frag[1][4];   // query fragments are re-read from shared memory: registers are the scarcer resource here
   const bf16* q_rows = q_tile + warp * 16 * ROW;
 
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int buffer = (tile - tile_lo) & 1;
-    if (tile < tile_hi) {
+  for (int step = 0; step < walked; ++step) {
+    const int tile = walked_tile(step, pre, tile_lo);
+    const int buffer = step & 1;
+    if (step + 1 < walked) {
       load_kv_tile<PBN>(k_tiles + (buffer ^ 1) * PBN * ROW, v_tiles + (buffer ^ 1) * PBN * ROW, tile_rows[buffer ^ 1], p,
-                        table, kv_head, (tile + 1) * PBN, lo, hi, own_values);
+                        table, kv_head, walked_tile(step + 1, pre, tile_lo) * PBN, lo, hi, own_values);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -356,7 +370,7 @@ __global__ void __launch_bounds__(THREADS, D <= 128 ? 4 : 2) portions_kernel(con
       const bf16* k_tile = k_tiles + buffer * PBN * ROW;
       const bf16* v_tile = own_values ? v_tiles + buffer * PBN * ROW : k_tile;
       scores<PBN / 8, false>(s, q_frag, q_rows, k_tile, 0, lane);
-      softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane, modified, p.scale, p.softcap, slope);
+      softmax_update<PBN / 8>(s, o, row_max, row_sum, first, last, tile * PBN, p.scale_log2, lane, modified, p.scale, p.softcap, slope, keep);
       accumulate<PBN / 8>(o, s, v_tile, 0, lane);
     }
     __syncthreads();
@@ -459,10 +473,15 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int head0 = kv_head * group + row_tile * 16;
   const int rows_here = min(16, group - row_tile * 16);
   const int tile_lo = first_key / BN, tile_hi = last_key / BN;
+  // The walk: the tiles of the kept first keys that lie before the window's (none without such keys), then the
+  // window's.  my_lo .. my_hi count tiles of the walk; `at(v)` is tile v's number in the sequence.
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int pre = tiles_before_window(keep, p.window, tile_lo, BN);
+  auto at = [&](int v) -> int { return walked_tile(v, pre, tile_lo); };
   // the tiles are dealt out as evenly as they go: no two splits differ by more than one
-  const int tiles = tile_hi - tile_lo + 1;
-  const int my_lo = tile_lo + static_cast<int>(static_cast<long long>(split) * tiles / p.splits);
-  const int my_hi = tile_lo + static_cast<int>(static_cast<long long>(split + 1) * tiles / p.splits) - 1;
+  const int tiles = pre + tile_hi - tile_lo + 1;
+  const int my_lo = static_cast<int>(static_cast<long long>(split) * tiles / p.splits);
+  const int my_hi = static_cast<int>(static_cast<long long>(split + 1) * tiles / p.splits) - 1;
 
   float o[MY_PAIRS][2][4];   // rows lane/4 and lane/4 + 8 of this warp's 16-column blocks
 #pragma unroll
@@ -493,7 +512,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     if (lane >= pages_per_tile) return -1;
     const int block = tile * pages_per_tile + lane;
     const int lo = block << p.page_shift, hi = lo + p.page_size - 1;
-    if (hi < first_key || lo > last_key || block >= p.max_blocks) return -1;
+    if ((hi < first_key && lo >= keep) || lo > last_key || block >= p.max_blocks) return -1;
     return table[block];   // used (and checked) a round later: nothing here waits for the load
   };
   auto issue_pages = [&](int stage, int page_of_lane, bool after_stores) {   // the loading warp, all lanes
@@ -533,14 +552,14 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     if (warp == SW) {
 #pragma unroll
       for (int ahead = 0; ahead < ST - 1; ++ahead)
-        if (my_lo + ahead <= my_hi) issue_pages(ahead, lookup_page_of_lane(my_lo + ahead), false);
+        if (my_lo + ahead <= my_hi) issue_pages(ahead, lookup_page_of_lane(at(my_lo + ahead)), false);
     }
   } else if (my_lo <= my_hi) {
     // rows of the first ST - 1 tiles without the newest key, and their copies, ahead of the wait
 #pragma unroll
     for (int ahead = 0; ahead < ST - 1; ++ahead)
       if (my_lo + ahead <= my_hi)
-        locate_tile<BN>(tile_rows[ahead], p, table, kv_head, (my_lo + ahead) * BN, first_key, last_key, last_key);
+        locate_tile<BN>(tile_rows[ahead], p, table, kv_head, at(my_lo + ahead) * BN, first_key, last_key, last_key);
     __syncthreads();
     // one commit group per tile, also when there is no tile left, so that the count is uniform
 #pragma unroll
@@ -558,7 +577,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       cp_async16(q_tile + row * ROW + chunk * 8, src, valid);
     }
     // the newest key, when its tile is one of those copied above
-    const int newest_tile = last_key / BN;
+    const int newest_tile = tiles - 1;   // of the walk: the window's last tile
     const bool newest_copied = newest_tile >= my_lo && newest_tile <= my_hi && newest_tile - my_lo < ST - 1;
     if (PAGES && newest_copied)   // its page must have landed before the row is replaced
       bw::mbar_wait(&tile_full[newest_tile - my_lo], 0, &give_up, p.status, ERR_TILE_WAIT);
@@ -568,20 +587,20 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       const bool valid = page >= 0 && page < p.num_pages;
       const size_t offset = valid ? (static_cast<size_t>(page) * p.page_size + (last_key - block * p.page_size)) * p.num_kv_heads * D +
                                         static_cast<size_t>(kv_head) * D + threadIdx.x * 8 : 0;
-      const int stage = newest_tile - my_lo, key = last_key - newest_tile * BN;
+      const int stage = newest_tile - my_lo, key = last_key - tile_hi * BN;
       cp_async16(tile_chunk<PAGES>(k_tiles + stage * TILE, key, threadIdx.x * 8), p.k_cache + offset, valid);
       cp_async16(tile_chunk<PAGES>(v_tiles + stage * TILE, key, threadIdx.x * 8), p.v_cache + offset, valid);
     }
     cp_async_commit();
     if (!PAGES && my_lo + ST - 1 <= my_hi)   // copied by the first round of the loop
-      locate_tile<BN>(tile_rows[ST - 1], p, table, kv_head, (my_lo + ST - 1) * BN, first_key, last_key);
+      locate_tile<BN>(tile_rows[ST - 1], p, table, kv_head, at(my_lo + ST - 1) * BN, first_key, last_key);
     // The table lookup for a tile is issued one round before its rows are stored, which is
     // one more round before they are copied: no round waits for a lookup of its own.
     int pending_page = -1;
     if (!PAGES && my_lo + ST <= my_hi && threadIdx.x < BN)
-      pending_page = lookup_page(p, table, (my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
+      pending_page = lookup_page(p, table, at(my_lo + ST) * BN + threadIdx.x, first_key, last_key, -1);
     int page_ahead = -1;   // PAGES, loading warp: lane j's page of the tile that the next round loads
-    if (PAGES && warp == SW && my_lo + ST - 1 <= my_hi) page_ahead = lookup_page_of_lane(my_lo + ST - 1);
+    if (PAGES && warp == SW && my_lo + ST - 1 <= my_hi) page_ahead = lookup_page_of_lane(at(my_lo + ST - 1));
     cp_async_wait<0>();
     __syncthreads();
     unsigned q_frag[Q_IN_REGS ? KSTEPS : 1][4];
@@ -590,12 +609,13 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       for (int kk = 0; kk < KSTEPS; ++kk)
         ldmatrix_x4(q_frag[Q_IN_REGS ? kk : 0], q_tile + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + kk * 16 + 8 * (lane >> 4));
     }
-    for (int tile = my_lo; tile <= my_hi; ++tile) {
-      const int buffer = (tile - my_lo) % ST;
-      const int ahead = tile + ST - 1;
+    for (int walk = my_lo; walk <= my_hi; ++walk) {
+      const int tile = at(walk);   // the tile's number in the sequence: its keys' positions
+      const int buffer = (walk - my_lo) % ST;
+      const int ahead = walk + ST - 1;
       // this tile has arrived; every warp is done with the tile before (its buffer is loaded into
       // next), and, in the first round, with reading the query out of the space the probabilities take
-      if (PAGES) bw::mbar_wait(&tile_full[buffer], ((tile - my_lo) / ST) & 1, &give_up, p.status, ERR_TILE_WAIT);
+      if (PAGES) bw::mbar_wait(&tile_full[buffer], ((walk - my_lo) / ST) & 1, &give_up, p.status, ERR_TILE_WAIT);
       else cp_async_wait<ST - 2>();
       __syncthreads();
       if (PAGES && give_up) break;   // a load that never landed is reported, not waited for; all leave together
@@ -607,15 +627,15 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           for (int c = threadIdx.x; c < BN * CHUNKS; c += NT) {
             const int key = c / CHUNKS, chunk = c - key * CHUNKS;
             const int position = tile * BN + key;
-            if (position < first_key || position > last_key)
+            if ((position < first_key && position >= keep) || position > last_key)
               *reinterpret_cast<uint4*>(tile_chunk<PAGES>(v_tiles + buffer * TILE, key, chunk * 8)) = make_uint4(0u, 0u, 0u, 0u);
           }
           __syncthreads();
         }
         if (warp == SW) {   // the loading warp: the next tile's loads, then on to the next round's barrier
           if (ahead <= my_hi) {
-            issue_pages((ahead - my_lo) % ST, page_ahead, (ahead - ST) * BN < first_key);
-            page_ahead = ahead + 1 <= my_hi ? lookup_page_of_lane(ahead + 1) : -1;   // used one round from now
+            issue_pages((ahead - my_lo) % ST, page_ahead, at(ahead - ST) * BN < first_key);
+            page_ahead = ahead + 1 <= my_hi ? lookup_page_of_lane(at(ahead + 1)) : -1;   // used one round from now
           }
           continue;
         }
@@ -626,9 +646,9 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       if (!PAGES) cp_async_commit();
       if (!PAGES && threadIdx.x < BN) {
         if (ahead + 1 <= my_hi)   // read in the next round, after its opening barrier
-          tile_rows[(ahead + 1 - my_lo) % (ST + 1)][threadIdx.x] = row_of(p, kv_head, (ahead + 1) * BN + threadIdx.x, pending_page);
+          tile_rows[(ahead + 1 - my_lo) % (ST + 1)][threadIdx.x] = row_of(p, kv_head, at(ahead + 1) * BN + threadIdx.x, pending_page);
         if (ahead + 2 <= my_hi)
-          pending_page = lookup_page(p, table, (ahead + 2) * BN + threadIdx.x, first_key, last_key, -1);
+          pending_page = lookup_page(p, table, at(ahead + 2) * BN + threadIdx.x, first_key, last_key, -1);
       }
       bf16* k_tile = k_tiles + buffer * TILE;
       bf16* v_tile = v_tiles + buffer * TILE;
@@ -655,7 +675,7 @@ single_token_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = tile * BN + key0 + (lane & 3) * 2 + (e & 1);
-        const bool seen = key >= first_key && key <= last_key;
+        const bool seen = (key >= first_key || key < keep) && key <= last_key;
         const float value = modified ? modified_score(sc[e], p.scale, p.softcap, slope[e >> 1], last_key - key)
                                      : sc[e] * p.scale_log2;
         sc[e] = seen ? value : -INFINITY;
@@ -934,15 +954,18 @@ SHRIKE_API int shrike_attention_bf16_resident_ctas() {
 // `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
 // softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
 // `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
-SHRIKE_API int shrike_paged_attention_bf16_sinks(const void* q, const void* k_cache, const void* v_cache,
-                                                 const int* block_table, int max_blocks, const int* q_start,
-                                                 const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
-                                                 int page_size, int num_pages, float scale, int window, void* out,
-                                                 int has_single, int has_portions, int max_q_len, int splits,
-                                                 int cluster, float* scratch, int* arrivals, int* status,
-                                                 float softcap, const float* slopes, const float* sinks, cudaStream_t stream) {
+// `keep_first` (with a window): the sequence's first `keep_first` keys stay visible to every later query.
+SHRIKE_API int shrike_paged_attention_bf16_kept(const void* q, const void* k_cache, const void* v_cache,
+                                                const int* block_table, int max_blocks, const int* q_start,
+                                                const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                                int page_size, int num_pages, float scale, int window, void* out,
+                                                int has_single, int has_portions, int max_q_len, int splits,
+                                                int cluster, float* scratch, int* arrivals, int* status,
+                                                float softcap, const float* slopes, const float* sinks, int keep_first,
+                                                cudaStream_t stream) {
   using namespace bf16attn;
   if (num_seqs <= 0) return SHRIKE_OK;
+  if (keep_first < 0) return SHRIKE_BAD_ARGUMENT;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || max_blocks <= 0 ||
       num_seqs > 65535 || num_heads > 65535)
     return SHRIKE_BAD_ARGUMENT;
@@ -987,6 +1010,7 @@ SHRIKE_API int shrike_paged_attention_bf16_sinks(const void* q, const void* k_ca
   p.softcap = softcap > 0.f ? softcap : 0.f;
   p.slopes = slopes;
   p.sinks = sinks;
+  p.keep_first = window > 0 ? keep_first : 0;
   p.partial_out = scratch;
   p.partial_ml = scratch ? scratch + static_cast<size_t>(num_seqs) * num_heads * (p.splits / p.cluster) * D : nullptr;
   p.arrivals = arrivals;
@@ -1009,6 +1033,19 @@ SHRIKE_API int shrike_paged_attention_bf16_sinks(const void* q, const void* k_ca
     launch_dependent(portions_kernel, grid, THREADS, PORTIONS_SMEM, stream, p);
   }
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_bf16_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                 const int* block_table, int max_blocks, const int* q_start,
+                                                 const int* ctx_len, int num_seqs, int num_heads, int num_kv_heads,
+                                                 int page_size, int num_pages, float scale, int window, void* out,
+                                                 int has_single, int has_portions, int max_q_len, int splits,
+                                                 int cluster, float* scratch, int* arrivals, int* status,
+                                                 float softcap, const float* slopes, const float* sinks, cudaStream_t stream) {
+  return shrike_paged_attention_bf16_kept(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_seqs,
+                                          num_heads, num_kv_heads, page_size, num_pages, scale, window, out, has_single,
+                                          has_portions, max_q_len, splits, cluster, scratch, arrivals, status, softcap,
+                                          slopes, sinks, 0, stream);
 }
 
 SHRIKE_API int shrike_paged_attention_bf16_scores(const void* q, const void* k_cache, const void* v_cache,

@@ -226,6 +226,10 @@ class CudaOps:
             [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P, _P]
         )
         lib.shrike_paged_attention_bf16_sinks.restype = _I
+        lib.shrike_paged_attention_bf16_kept.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 5 + [_F, _I, _P] + [_I] * 5 + [_P, _P, _P, _F, _P, _P, _I, _P]
+        )
+        lib.shrike_paged_attention_bf16_kept.restype = _I
         lib.shrike_attention_single_token_pages.argtypes = [_I]
         lib.shrike_attention_single_token_pages.restype = None
         lib.shrike_attention_bf16_resident_ctas.restype = _I
@@ -558,7 +562,7 @@ class CudaOps:
                 raise KernelError("attention takes a window or a chunk, not both")
             window = -int(chunk)   # the kernels' one number: > 0 a window, < 0 runs of that many positions
         keep_first = int(keep_first) if window and window > 0 else 0
-        if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM or keep_first:
+        if self.dtype == torch.float32 or head_dim > build.TENSOR_CORE_HEAD_DIM:
             self.launches += 1
             _check(lib.shrike_paged_attention_generic_kept(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start),
@@ -572,9 +576,11 @@ class CudaOps:
                 raise KernelError("one distance slope per query head")
         plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
                                    q.shape[0], q_lens)
-        self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
+        # kept first keys: the tcgen05 portions kernel walks one run of tiles, so such layers' portions take the mma.sync one
+        tc_portions = plan.tc_portions and not keep_first
+        self.launches += plan.has_single + plan.has_portions + (1 if tc_portions and plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
-        if plan.tc_portions:
+        if tc_portions:
             _check(lib.shrike_paged_attention_tc_portions_sinks(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
@@ -584,11 +590,11 @@ class CudaOps:
             has_portions = 0
             if not plan.has_single:
                 return
-        _check(lib.shrike_paged_attention_bf16_sinks(
+        _check(lib.shrike_paged_attention_bf16_kept(
             _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
             num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
             plan.has_single, has_portions, max_q_len, plan.splits, plan.cluster, _ptr(plan.scratch), _ptr(plan.arrivals),
-            _ptr(self.status), softcap or 0.0, _ptr(slopes), _ptr(sinks), self._stream()),
+            _ptr(self.status), softcap or 0.0, _ptr(slopes), _ptr(sinks), keep_first, self._stream()),
             "paged_attention_bf16")
 
     def portion_tiles(self, q_lens, skip_single, rows) -> int:
