@@ -477,7 +477,7 @@ def run_mixed(args) -> dict:
 
     torch.cuda.set_device(0)
     design = getattr(args, "arch", "qwen2")   # the same workload on another decoder at the same widths
-    sadodra = design in ("sadodra", "vupitar", "kavedra")
+    sadodra = design in ("sadodra", "vupitar", "kavedra", "setotar")
     if sadodra:
         from shrike_b200.shapes import shape_config
 
@@ -828,7 +828,7 @@ def run_timeline(args) -> dict:
 
 
 def run_design(args) -> dict:
-    """A design (--arch sadodra, the default here, vupitar or kavedra) beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
+    """A design (--arch sadodra, the default here, vupitar, kavedra or setotar; the last also beside Vupitar) beside the Qwen2 decoder of the same widths, layer count and vocabulary (the
     closest model this engine serves), random weights: one 2,048-token prompt in one step, and decoding
     at --batch sequences of --context tokens, device-timed through the step function and the sampling
     kernel; for each, the kernels of one step by the time they take (CUPTI activity records).
@@ -962,8 +962,16 @@ def run_design(args) -> dict:
     sampler = ClockSampler()
     sampler.start()
     t0 = time.perf_counter()
-    results = [measure(f"{design.capitalize()} at Qwen2.5-{args.design.upper()} widths", ours),
-               measure(f"Qwen2.5-{args.design.upper()} shape", theirs)]
+    results = [measure(f"{design.capitalize()} at Qwen2.5-{args.design.upper()} widths", ours)]
+    if design == "setotar":
+        # the design it is closest to among those served: attention beside a recurrent memory in one layer, routed experts
+        likeness = dict(shape_config(f"vupitar-{args.design}"))
+        if args.layers:
+            loop = likeness.get("loop")
+            extra = (loop["stop"] - loop["start"]) * (loop["times"] - 1) if loop else 0
+            likeness["layers"] = likeness["layers"][: max(args.layers - extra, loop["stop"] if loop else 1)]
+        results.append(measure(f"Vupitar at Qwen2.5-{args.design.upper()} widths", likeness))
+    results.append(measure(f"Qwen2.5-{args.design.upper()} shape", theirs))
     sampler.stop()
     return {"case": "design", "design": design.capitalize(), "closest": "Qwen2ForCausalLM", "dtype": "bf16",
             "data": "synthetic: seeded random weights and uniform random token ids", "peaks": peaks,
@@ -993,7 +1001,7 @@ def main():
     parser.add_argument("--context", type=int, default=1024, help="tokens each sequence holds when decoding is timed")
     parser.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                         help="decode: the headline line; mixed: 64 requests through the scheduler at 1.5B shape")
-    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra", "vupitar", "kavedra"],
+    parser.add_argument("--arch", default="qwen2", choices=["qwen2", "sadodra", "vupitar", "kavedra", "setotar"],
                         help="--workload mixed: the decoder the 64 requests run on (all at Qwen2.5-1.5B widths); "
                              "--case design: the design that is set beside the Qwen2 decoder (default there: sadodra)")
     parser.add_argument("--num-blocks", type=int, default=0, help="cache pages for --workload mixed (few pages force preemption)")
