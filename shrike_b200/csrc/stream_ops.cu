@@ -13,7 +13,7 @@
 //                    projected values before a portion's first token taken from the request's state (zeros at a
 //                    sequence's start); short_conv_keep leaves the last T - 1 projected values there.
 //   gated_scan       per head S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with q = silu(.) and
-//                    f = lower + (1 - lower) sigmoid(. + bias), token by token with the state slice on chip; for long
+//                    f = lower + (1 - lower) sigmoid(. + bias), token by token with the state slice in registers; for long
 //                    portions in three launches over runs of tokens (every run from a zero state and its decay, the
 //                    runs' states carried in order, every run again from the state it starts from).
 //   head_rms         every head of a row over its root mean square, times one weight of the head's size.
@@ -243,7 +243,7 @@ struct ScanArgs {
   const int* q_start;
   const int* state_slot;
   float* out;             // [N][H Dv]
-  int heads, dim, vdim, head_stride, cols, row_groups, num_slots;
+  int heads, dim, vdim, head_stride, cols, row_groups, num_slots;   // row_groups: the lanes of a warp that share a column
   // runs of tokens (0: the whole portion is one walk from the slot's state)
   int run;                // tokens a run holds
   int phase;              // 1: every run from a zero state, leaves its state and its decay; 3: every run from `run_state`
@@ -256,20 +256,28 @@ struct ScanArgs {
 __device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // One CTA owns `cols` value columns of one head's state for one sequence (or one run of its tokens) and walks the
-// tokens in order.  Thread (g, j) holds rows g, g + G, ... of column j; S lives in shared memory as S[d * cols + j].
-__global__ void gated_scan_kernel(const ScanArgs a) {
-  extern __shared__ float scan_shared[];
+// tokens in order with the state in registers.  A column is shared by `lanes` neighbouring lanes of a warp (a power of
+// two, `row_groups` in the arguments): lane g of them holds rows g R .. g R + R - 1 of the column, so a token costs a
+// thread R multiply-adds for the state and R for its share of q . S, the shares meet by shuffles, and no barrier
+// falls inside the walk.  Tokens are staged SCAN_TOKENS at a time: q, f and 1 - f of the head (a lane's rows side by
+// side, each lane's run padded by four floats so that the lanes' 16-byte loads fall into different banks) and the
+// CTA's columns of v.
+template <int R>
+__global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
+  extern __shared__ __align__(16) float scan_shared[];
   let_dependents_start();
   wait_for_previous();
-  const int D = a.dim, cols = a.cols, G = a.row_groups;
-  float* S = scan_shared;                       // [D][cols]
-  float* q = S + static_cast<size_t>(D) * cols; // [SCAN_TOKENS][D]
-  float* f = q + SCAN_TOKENS * D;               // [SCAN_TOKENS][D]
-  float* k = f + SCAN_TOKENS * D;               // [SCAN_TOKENS][D]: 1 - f
-  float* v = k + SCAN_TOKENS * D;               // [SCAN_TOKENS][cols]
-  float* red = v + SCAN_TOKENS * cols;          // [2][G][cols]
-  float* decay = red + 2 * G * cols;            // [D]: phase 1, the product of the run's gates
-  const int j = threadIdx.x % cols, g = threadIdx.x / cols;
+  const int D = a.dim, cols = a.cols, lanes = a.row_groups;
+  constexpr int PITCH = R + 4;                  // floats between the runs of two neighbouring lanes
+  const int padded = lanes * PITCH;             // floats of one staged token's q (or f, or 1 - f)
+  float* q = scan_shared;                       // [SCAN_TOKENS][padded]
+  float* f = q + SCAN_TOKENS * padded;
+  float* k = f + SCAN_TOKENS * padded;          // 1 - f
+  float* v = k + SCAN_TOKENS * padded;          // [SCAN_TOKENS][cols]
+  float* decay = v + SCAN_TOKENS * cols;        // [D]: phase 1, the product of the run's gates
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane % lanes;
+  const int j = warp * (32 / lanes) + lane / lanes;     // this thread's column of the CTA's
   const int head = blockIdx.y, col0 = blockIdx.x * cols;
   const int cols_here = min(cols, a.vdim - col0);
   int seq, first, length, run_index = -1;
@@ -289,24 +297,29 @@ __global__ void gated_scan_kernel(const ScanArgs a) {
   const int slot = a.state_slot[seq];
   const bool held = slot >= 0 && slot < a.num_slots;
   const int HV = a.heads * a.vdim;
+  const bool mine = j < cols_here;
   if (!held) {   // a padding row: zeros out, nothing kept
-    if (a.phase != 1)
-      for (int t = g; t < length; t += G)
-        if (j < cols_here) a.out[static_cast<size_t>(first + t) * HV + head * a.vdim + col0 + j] = 0.f;
+    if (a.phase != 1 && g == 0 && mine)
+      for (int t = 0; t < length; ++t) a.out[static_cast<size_t>(first + t) * HV + head * a.vdim + col0 + j] = 0.f;
     return;
   }
   float* slot_state = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.head_stride;
   float* run_state = a.run > 0 ? a.run_state + (static_cast<size_t>(run_index) * a.heads + head) * D * a.vdim : nullptr;
   const float* from = a.run == 0 ? slot_state : (a.phase == 3 ? run_state : nullptr);
-  for (int d = g; d < D; d += G)
-    if (j < cols_here) S[d * cols + j] = from != nullptr ? from[static_cast<size_t>(d) * a.vdim + col0 + j] : 0.f;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int d = g * R + r;
+    S[r] = from != nullptr && mine && d < D ? from[static_cast<size_t>(d) * a.vdim + col0 + j] : 0.f;
+  }
+  // rows past the head's own (the lanes' runs cover lanes * R >= D of them) stay zero in q, f and 1 - f
+  for (int i = threadIdx.x; i < 3 * SCAN_TOKENS * padded; i += blockDim.x) q[i] = 0.f;
   if (a.phase == 1)
     for (int d = threadIdx.x; d < D; d += blockDim.x) decay[d] = 1.f;
   const int q_col = head * D, f_col = a.heads * D + head * D, v_col = 2 * a.heads * D + head * a.vdim + col0;
-  int parity = 0;
   for (int t0 = 0; t0 < length; t0 += SCAN_TOKENS) {
     const int here = min(SCAN_TOKENS, length - t0);
-    __syncthreads();   // the tokens staged before are used up
+    __syncthreads();   // the tokens staged before are used up (and, the first time, the zeros are in place)
     for (int i = threadIdx.x; i < here * D; i += blockDim.x) {
       const int t = i / D, d = i - t * D;
       const float* row = a.fused + static_cast<size_t>(first + t0 + t) * a.total;
@@ -314,60 +327,67 @@ __global__ void gated_scan_kernel(const ScanArgs a) {
       float zf = sum_partials(row + f_col + d, a.stride, a.partials);
       if (a.f_bias != nullptr) zf = __fadd_rn(zf, a.f_bias[head * D + d]);
       const float low = a.lower != nullptr ? a.lower[head * D + d] : 0.f;
+      const int at = t * padded + (d / R) * PITCH + d % R;
       // 1 - f = (1 - lower) (1 - sigmoid(z)) = (1 - lower) sigmoid(-z): formed so, a gate close to one keeps the
       // digits of what it lets in, which 1 - f computed from f would lose
-      q[t * D + d] = zq * sigmoid32(zq);
-      f[t * D + d] = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
-      k[t * D + d] = (1.0f - low) * sigmoid32(-zf);
+      q[at] = zq * sigmoid32(zq);
+      f[at] = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
+      k[at] = (1.0f - low) * sigmoid32(-zf);
     }
     for (int i = threadIdx.x; i < here * cols; i += blockDim.x) {
       const int t = i / cols, c = i - t * cols;
       v[t * cols + c] = c < cols_here ? sum_partials(a.fused + static_cast<size_t>(first + t0 + t) * a.total + v_col + c, a.stride, a.partials) : 0.f;
     }
     __syncthreads();
-    if (a.phase == 1) {
-      // the run's own addition to the state and the product of its gates; the outputs come in phase 3
-      for (int t = 0; t < here; ++t) {
-        const float value = v[t * cols + j];
-        for (int d = g; d < D; d += G) S[d * cols + j] = __fmaf_rn(f[t * D + d], S[d * cols + j], k[t * D + d] * value);
+    if (a.phase == 1 && blockIdx.x == 0)
+      for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float p = decay[d];
+        for (int t = 0; t < here; ++t) p *= f[t * padded + (d / R) * PITCH + d % R];
+        decay[d] = p;
       }
-      if (blockIdx.x == 0)
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-          float p = decay[d];
-          for (int t = 0; t < here; ++t) p *= f[t * D + d];
-          decay[d] = p;
-        }
-      continue;
-    }
     for (int t = 0; t < here; ++t) {
       const float value = v[t * cols + j];
+      const float4* f4 = reinterpret_cast<const float4*>(f + t * padded + g * PITCH);
+      const float4* k4 = reinterpret_cast<const float4*>(k + t * padded + g * PITCH);
+      const float4* q4 = reinterpret_cast<const float4*>(q + t * padded + g * PITCH);
       float partial = 0.f;
-      for (int d = g; d < D; d += G) {
-        const float s = __fmaf_rn(f[t * D + d], S[d * cols + j], k[t * D + d] * value);
-        S[d * cols + j] = s;
-        partial = __fmaf_rn(s, q[t * D + d], partial);
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 ff = f4[r >> 2], kk = k4[r >> 2], qq = q4[r >> 2];
+        S[r] = __fmaf_rn(ff.x, S[r], kk.x * value);
+        S[r + 1] = __fmaf_rn(ff.y, S[r + 1], kk.y * value);
+        S[r + 2] = __fmaf_rn(ff.z, S[r + 2], kk.z * value);
+        S[r + 3] = __fmaf_rn(ff.w, S[r + 3], kk.w * value);
+        partial = __fmaf_rn(S[r], qq.x, partial);
+        partial = __fmaf_rn(S[r + 1], qq.y, partial);
+        partial = __fmaf_rn(S[r + 2], qq.z, partial);
+        partial = __fmaf_rn(S[r + 3], qq.w, partial);
       }
-      red[(parity * G + g) * cols + j] = partial;
-      __syncthreads();
-      if (g == 0 && j < cols_here) {
-        float sum = red[(parity * G) * cols + j];
-        for (int r = 1; r < G; ++r) sum = __fadd_rn(sum, red[(parity * G + r) * cols + j]);
-        a.out[static_cast<size_t>(first + t0 + t) * HV + head * a.vdim + col0 + j] = sum;
-      }
-      parity ^= 1;
+      if (a.phase == 1) continue;   // a run's own addition to the state: its outputs come in phase 3
+      for (int offset = lanes >> 1; offset > 0; offset >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, offset);
+      if (g == 0 && mine) a.out[static_cast<size_t>(first + t0 + t) * HV + head * a.vdim + col0 + j] = partial;
     }
   }
-  __syncthreads();
   if (a.phase == 1) {
-    for (int d = g; d < D; d += G)
-      if (j < cols_here) run_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[d * cols + j];
+    if (mine) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int d = g * R + r;
+        if (d < D) run_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[r];
+      }
+    }
+    __syncthreads();
     if (blockIdx.x == 0)
       for (int d = threadIdx.x; d < D; d += blockDim.x) a.run_decay[(static_cast<size_t>(run_index) * a.heads + head) * D + d] = decay[d];
     return;
   }
-  if (a.run == 0)
-    for (int d = g; d < D; d += G)
-      if (j < cols_here) slot_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[d * cols + j];
+  if (a.run == 0 && mine) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = g * R + r;
+      if (d < D) slot_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[r];
+    }
+  }
 }
 
 // The index of every sequence's first run, from the batch's lengths: one thread, a few hundred sequences at most.
@@ -488,18 +508,19 @@ SHRIKE_API int shrike_short_conv(const float* fused, int partials, long long str
   return shrike_launch_status();
 }
 
-// Value columns a CTA of the scan takes and the row groups its threads form, for heads of dim x vdim.
-static inline bool scan_shape(int dim, int vdim, int* cols, int* groups, size_t* smem) {
-  const size_t limit = static_cast<size_t>(shrike_device().max_smem);
-  for (int c = min(64, vdim); c >= 1; c = c > 8 ? c / 2 : c - 1) {
-    const int g = max(1, min(dim, 256 / c));
-    const size_t need = (static_cast<size_t>(dim) * c + 3 * SCAN_TOKENS * dim + SCAN_TOKENS * c + 2 * g * c + dim) * sizeof(float);
-    if (need <= limit) {
-      *cols = c; *groups = g; *smem = need;
-      return true;
-    }
-  }
-  return false;
+// How the scan is laid out for heads of dim x vdim: R rows of a column a thread (32, or 8 for small heads), the
+// lanes that share a column (a power of two covering dim), the columns a CTA of up to eight warps takes.
+struct ScanShape { int rows, lanes, cols, threads; size_t smem; };
+static inline bool scan_shape(int dim, int vdim, ScanShape* shape) {
+  const int rows = dim >= 64 ? 32 : 8;
+  int lanes = 1;
+  while (lanes * rows < dim) lanes *= 2;
+  if (lanes > 32) return false;
+  const int per_warp = 32 / lanes;
+  const int warps = max(1, min(8, (vdim + per_warp - 1) / per_warp));
+  shape->rows = rows; shape->lanes = lanes; shape->cols = per_warp * warps; shape->threads = warps * 32;
+  shape->smem = (static_cast<size_t>(3) * SCAN_TOKENS * lanes * (rows + 4) + static_cast<size_t>(SCAN_TOKENS) * shape->cols + dim) * sizeof(float);
+  return shape->smem <= static_cast<size_t>(shrike_device().max_smem);
 }
 
 SHRIKE_API long long shrike_gated_scan_runs(int n, int num_seqs, int run) { return (static_cast<long long>(n) + run - 1) / run + num_seqs; }
@@ -517,26 +538,26 @@ SHRIKE_API int shrike_gated_scan(const float* fused, int partials, long long str
   if (heads < 1 || heads > 65535 || num_seqs > 65535 || dim < 1 || vdim < 1 || partials < 1 || head_stride < dim * vdim ||
       total < heads * (2 * dim + vdim))
     return SHRIKE_BAD_ARGUMENT;
-  int cols = 0, groups = 0;
-  size_t smem = 0;
-  if (!scan_shape(dim, vdim, &cols, &groups, &smem)) return SHRIKE_BAD_ARGUMENT;
+  ScanShape shape;
+  if (!scan_shape(dim, vdim, &shape)) return SHRIKE_BAD_ARGUMENT;   // heads of more than 1,024 rows
   ScanArgs a = {fused, stride, partials, total, f_bias, lower, state, q_start, state_slot, out, heads, dim, vdim,
-                head_stride, cols, groups, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs};
-  if (smem > 48 * 1024) cudaFuncSetAttribute(gated_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  const unsigned slices = static_cast<unsigned>((vdim + cols - 1) / cols);
-  const unsigned threads = static_cast<unsigned>(cols * groups);
+                head_stride, shape.cols, shape.lanes, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs};
+  void (*kernel)(ScanArgs) = shape.rows == 32 ? gated_scan_kernel<32> : gated_scan_kernel<8>;
+  if (shape.smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shape.smem));
+  const unsigned slices = static_cast<unsigned>((vdim + shape.cols - 1) / shape.cols);
+  const unsigned threads = static_cast<unsigned>(shape.threads);
   if (run <= 0 || run_state == nullptr || run_decay == nullptr || run_first == nullptr || num_runs < 1) {
-    launch_dependent(gated_scan_kernel, dim3(slices, heads, num_seqs), threads, smem, stream, a);
+    launch_dependent(kernel, dim3(slices, heads, num_seqs), threads, shape.smem, stream, a);
     return shrike_launch_status();
   }
   if (num_runs > 65535) return SHRIKE_BAD_ARGUMENT;
   a.run = run; a.run_state = run_state; a.run_decay = run_decay; a.run_first = run_first;
   launch_dependent(gated_scan_plan_kernel, 1, 32, 0, stream, a);
   a.phase = 1;
-  launch_dependent(gated_scan_kernel, dim3(slices, heads, num_runs), threads, smem, stream, a);
+  launch_dependent(kernel, dim3(slices, heads, num_runs), threads, shape.smem, stream, a);
   launch_dependent(gated_scan_carry_kernel, dim3((dim * vdim + 255) / 256, heads, num_seqs), 256, 0, stream, a);
   a.phase = 3;
-  launch_dependent(gated_scan_kernel, dim3(slices, heads, num_runs), threads, smem, stream, a);
+  launch_dependent(kernel, dim3(slices, heads, num_runs), threads, shape.smem, stream, a);
   return shrike_launch_status();
 }
 

@@ -59,7 +59,7 @@ _LIMITS = {
     "matrix_memory_scan": "a positive gate cap, at most 65535 sequences and heads, the row at least as wide as q, k, v, gate and both gate columns, the state's heads at least dim * vdim + dim + 1 floats",
     "stream_norm": "1 to 8 streams, at most four pending sums, a row that fits an SM's shared memory",
     "short_conv": "1 to 32 taps, at most 65535 sequences, the convolved channels the projection's first columns",
-    "gated_scan": "at most 65535 sequences, heads and runs of tokens, the row at least as wide as q, f and v, the state's heads at least dim * vdim floats",
+    "gated_scan": "heads of at most 1024 rows, at most 65535 sequences, heads and runs of tokens, the row at least as wide as q, f and v, the state's heads at least dim * vdim floats",
     "route_top": "at most 1024 experts, 1 <= top <= experts, the weights [N, experts] or [N, experts + 1]",
     "act_mul_blocks": "experts * each columns at most, the rest the shared expert's, which needs the weights' last column",
     "paged_attention_bf16": "at most 65535 sequences and heads, heads a multiple of kv heads, at most 32 splits",
