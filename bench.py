@@ -688,6 +688,93 @@ def run_case(args) -> dict:
         # part of the outputs 2 x 64 x dim x vdim (2 flops a multiply-add)
         work = {"bytes": seqs * mh * (md * mv + md) * 4 * 2 + n * total * 4} if single else \
                {"flops": 2.0 * seqs * mh * chunks * (64 * 64 * md + 64 * 64 * mv + 2 * 64 * md * mv)}
+    elif args.case in ("gated_scan", "gated_scan_single"):
+        # the gated linear recurrence at the 7B-width shape (8 heads of 128 x 128): one prompt of --prefill-tokens tokens
+        # (runs of 64 tokens, each walked twice), or --batch sequences one token each (one walk)
+        lh, ld, lv = 8, d, d
+        single = args.case.endswith("_single")
+        seqs, q_len = (tokens, 1) if single else (1, args.prefill_tokens)
+        n = seqs * q_len
+        total = -(-(2 * lh * ld + lh * lv) // 16) * 16
+        fused = torch.randn(n, total, device=dev, dtype=torch.float32)
+        bias, lower = torch.randn(lh * ld, device=dev), torch.rand(lh * ld, device=dev) * 0.9
+        state = torch.zeros(seqs, lh, ld * lv, device=dev)
+        q_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        out = torch.empty(n, lh * lv, device=dev)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.gated_scan(fused, bias, lower, state, q_start, slots, out, seqs, lh, ld, lv, q_lens=[q_len] * seqs)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        # a token and head: dim x vdim multiply-adds for the state and as many for the output (2 flops each); a prompt's
+        # runs are walked twice, which the count leaves out (it is the recurrence's own arithmetic)
+        work = {"bytes": seqs * lh * ld * lv * 4 * 2 + n * total * 4 + n * lh * lv * 4} if single else \
+               {"flops": 4.0 * n * lh * ld * lv}
+    elif args.case == "stream_norm":
+        # --batch rows of four streams of the 7B width with a two-term pending result and a layer scale
+        count = 4
+        streams = torch.randn(tokens, count, h, device=dev)
+        terms = [(torch.randn(tokens, h, device=dev), 1.0), (torch.randn(tokens, h, device=dev), 0.9)]
+        join = (torch.eye(count, device=dev) + 0.1, torch.ones(count, device=dev), torch.ones(h, device=dev))
+        in_w, weight = torch.ones(count, device=dev), torch.ones(h, device=dev)
+        out = torch.empty(tokens, h, device=dev, dtype=torch.bfloat16)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.stream_norm(streams, terms, join, in_w, weight, 1e-6, out)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": tokens * h * (2 * count * 4 + 2 * 4 + 2)}
+    elif args.case == "short_conv":
+        # --batch tokens of one sequence, the fused q | k | v projection of the 7B-width shape, four taps
+        channels = (heads + 2 * kv) * d
+        fused = torch.randn(tokens, channels, device=dev)
+        taps = torch.randn(channels, 4, device=dev)
+        state = torch.zeros(1, 3, channels, device=dev)
+        q_start = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+        out = torch.empty_like(fused)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.short_conv(fused, None, taps, state, q_start, torch.zeros(1, dtype=torch.int32, device=dev),
+                           torch.zeros(tokens, dtype=torch.int32, device=dev), out, 1, channels)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        work = {"bytes": tokens * channels * 4 * 2}
+    elif args.case in ("attention_single_kept", "attention_portions_kept"):
+        # a window of 4,096 keys that keeps the first four, soft-capped: --batch sequences of 8,192 keys one token each,
+        # or a prompt of --prefill-tokens
+        single = args.case.startswith("attention_single")
+        seqs = tokens if single else 1
+        ctx_len = 8192 if single else args.prefill_tokens
+        q_len = 1 if single else args.prefill_tokens
+        window = 4096
+        blocks = -(-ctx_len // BLOCK_SIZE)
+        keys = torch.randn(seqs * blocks + 8, BLOCK_SIZE, kv, d, device=dev, dtype=torch.bfloat16)
+        values = torch.randn_like(keys)
+        q = torch.randn(seqs * q_len, heads * d, device=dev, dtype=torch.bfloat16)
+        width = max(8, 1 << (blocks - 1).bit_length())
+        table = torch.full((seqs, width), -1, dtype=torch.int32, device=dev)
+        table[:, :blocks] = torch.arange(seqs * blocks, dtype=torch.int32, device=dev).view(seqs, blocks)
+        q_start = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        ctx = torch.full((seqs,), ctx_len, dtype=torch.int32, device=dev)
+        seq_of = torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len)
+        out = torch.empty_like(q)
+        for _ in range(6):
+            keep_busy()
+            start.record()
+            ops.paged_attention(q, keys, values, table, q_start, ctx, seq_of, heads, kv, d, d ** -0.5, window, out,
+                                max_q_len=q_len, min_q_len=q_len, q_lens=[q_len] * seqs, softcap=30.0, keep_first=4)
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3)
+        seen = sum(min(p + 1, window + 4) for p in range(ctx_len - q_len, ctx_len))
+        work = {"bytes": seqs * (window + 4) * 2 * kv * d * 2} if single else {"flops": 4.0 * heads * d * seen}
     elif args.case in ("attention_single", "attention_portions", "attention_single_scores", "attention_portions_scores",
                        "attention_single_latent", "attention_portions_latent", "attention_single_sink", "attention_portions_sink"):
         single = args.case.startswith("attention_single")
@@ -1015,7 +1102,8 @@ def main():
                              "gemm_qkv, attention_single, attention_portions (with _scores: soft-capped and distance-biased; with _latent: "
                              "one key/value head of 256 whose keys are its values; with _sink: a sink in every softmax), "
                              "branch_norm, tanh_norm, head_prep, matrix_memory (a prompt of --prefill-tokens), matrix_memory_single, "
-                             "decay_scan (a prompt of --prefill-tokens), decay_scan_single, latent_rope_store; "
+                             "decay_scan (a prompt of --prefill-tokens), decay_scan_single, latent_rope_store, gated_scan, gated_scan_single, "
+                             "stream_norm, short_conv, attention_single_kept, attention_portions_kept; "
                              "--batch gives tokens / sequences / rows.  timeline: per-kernel "
                              "times inside one captured decode step (--layers, default 6).  design: the Sadodra decoder "
                              "beside the Qwen2 decoder of equal widths (--design), prefill and decode")

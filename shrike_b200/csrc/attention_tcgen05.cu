@@ -130,6 +130,10 @@ struct Args {
   // optional: one learned number per head whose exponential is one more term of the softmax's denominator (a sink:
   // its share of the weight attends to nothing; taken as it is, without `scale`), added where a row's sum is final
   const float* sinks;
+  // with a window: the sequence's first `keep_first` keys stay visible to every later query.  The tiles that hold them
+  // and lie before the window's are one more key split of their own (the last of `splits`), so that a CTA still walks
+  // one run of tiles; its rows meet the window's in the second kernel.
+  int keep_first;
 };
 
 // Which (sequence, query tile) a CTA with work index `work` owns: sequences in order, each with its
@@ -252,15 +256,21 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const int hi = max(hi_0, hi_1);
   const int tile_hi = hi / KEYS;
   const int all_tiles = tile_hi - lo / KEYS + 1;
-  const int per = (all_tiles + args.splits - 1) / args.splits;
-  const int tile_lo = lo / KEYS + split * per;                  // this CTA's share: tiles tile_lo ... (none: an empty split)
-  const int last_tile = min(tile_hi, tile_lo + per - 1);
+  const int keep = args.window > 0 ? args.keep_first : 0;
+  const int window_splits = args.splits - (keep > 0 ? 1 : 0);   // the last split, with kept keys, is theirs
+  const bool kept_split = keep > 0 && split == window_splits;
+  const int per = (all_tiles + window_splits - 1) / window_splits;
+  // this CTA's share: tiles tile_lo ... last_tile (none: an empty split); the kept keys' split takes the tiles that
+  // hold them and lie wholly before the window's first
+  const int tile_lo = kept_split ? 0 : lo / KEYS + split * per;
+  const int last_tile = kept_split ? min((keep - 1) / KEYS, lo / KEYS - 1) : min(tile_hi, tile_lo + per - 1);
   const int count_0 = max(0, min(last_tile, hi_0 / KEYS) - tile_lo + 1);
   const int count_1 = rows_1 > 0 ? max(0, min(last_tile, hi_1 / KEYS) - tile_lo + 1) : 0;
   const int num_tiles = max(count_0, count_1);
   // the same in steps of 64 keys: a chain's last tile may need its first half only
-  const int steps_0 = count_0 > 0 ? min(2 * count_0, hi_0 / HALF_KEYS - 2 * tile_lo + 1) : 0;
-  const int steps_1 = count_1 > 0 ? min(2 * count_1, hi_1 / HALF_KEYS - 2 * tile_lo + 1) : 0;
+  const int last_step = kept_split ? (keep - 1) / HALF_KEYS : 0x3fffffff;   // the kept keys end here
+  const int steps_0 = count_0 > 0 ? min(min(2 * count_0, hi_0 / HALF_KEYS - 2 * tile_lo + 1), last_step + 1) : 0;
+  const int steps_1 = count_1 > 0 ? min(min(2 * count_1, hi_1 / HALF_KEYS - 2 * tile_lo + 1), last_step + 1) : 0;
 
   const unsigned users = (steps_0 > 0 ? 1u : 0u) + (steps_1 > 0 ? 1u : 0u);   // chains that read the key and value stages
   if (threadIdx.x == 0) {
@@ -429,6 +439,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int my_steps = chain == 0 ? steps_0 : steps_1;
     const int last = t < q_len ? pos0 + t : -1;
     const int first = first_visible_key(last, args.window);
+    const int keep = args.window > 0 ? args.keep_first : 0;
     const unsigned lane_base = static_cast<unsigned>(quarter * 32) << 16;
     const unsigned tmem_chain = sh->tmem_base + chain * CHAIN_COLS + lane_base, tmem_o = tmem_chain + O_COL;
     float row_max = -INFINITY, row_sum = 0.f;
@@ -475,7 +486,7 @@ portions_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int key = key_base + g * 32 + j;
-            if (key < first || key > last) v[g][j] = 0xff800000u;   // -inf
+            if ((key < first && key >= keep) || key > last) v[g][j] = 0xff800000u;   // -inf
           }
       }
       float part_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains of dependent instructions, not one
@@ -694,16 +705,19 @@ SHRIKE_API long long shrike_attention_tc_portions_scratch_floats(int num_tokens,
 // `softcap` > 0 and `slopes` (float32 [num_heads], or null) change a score s = scale * q.k to
 // softcap * tanh(s / softcap) and then to s - slopes[head] * (query position - key position).
 // `sinks` (float32 [num_heads], or null): exp(sinks[head]) is added to the softmax's denominator of every row.
-SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void* q, const void* k_cache, const void* v_cache,
-                                                         const int* block_table, int max_blocks, const int* q_start,
-                                                         const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
-                                                         int num_kv_heads, int page_size, int num_pages, float scale,
-                                                         int window, void* out, int skip_single, int max_q_len, int* status,
-                                                         int splits, float* scratch, int portion_tiles,
-                                                         const int* seq_of_token, float softcap, const float* slopes, const float* sinks,
-                                                         cudaStream_t stream) {
+// `keep_first` (with a window): the sequence's first `keep_first` keys stay visible; `splits` then counts one split
+// more than the window's keys are dealt to (at least 2), and the scratch is sized for all of them.
+SHRIKE_API int shrike_paged_attention_tc_portions_kept(const void* q, const void* k_cache, const void* v_cache,
+                                                        const int* block_table, int max_blocks, const int* q_start,
+                                                        const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
+                                                        int num_kv_heads, int page_size, int num_pages, float scale,
+                                                        int window, void* out, int skip_single, int max_q_len, int* status,
+                                                        int splits, float* scratch, int portion_tiles,
+                                                        const int* seq_of_token, float softcap, const float* slopes, const float* sinks,
+                                                        int keep_first, cudaStream_t stream) {
   using namespace tcattn;
   if (num_seqs <= 0 || num_tokens <= 0) return SHRIKE_OK;
+  if (keep_first < 0 || (keep_first > 0 && window > 0 && splits < 2)) return SHRIKE_BAD_ARGUMENT;
   if (splits < 1 || splits > 32 || (splits > 1 && (scratch == nullptr || seq_of_token == nullptr))) return SHRIKE_BAD_ARGUMENT;
   // query tiles of the batch's portions: the caller's count, or what `num_tokens` tokens in
   // `num_seqs` sequences can make at most
@@ -745,6 +759,7 @@ SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void* q, const voi
   args.softcap = softcap > 0.f ? softcap : 0.f;
   args.slopes = slopes;
   args.sinks = sinks;
+  args.keep_first = window > 0 ? keep_first : 0;
   args.splits = splits;
   args.num_tokens = num_tokens;
   args.num_seqs = num_seqs;
@@ -759,6 +774,20 @@ SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void* q, const voi
     if (err != cudaSuccess) return static_cast<int>(err);
   }
   return shrike_launch_status();
+}
+
+SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                         const int* block_table, int max_blocks, const int* q_start,
+                                                         const int* ctx_len, int num_tokens, int num_seqs, int num_heads,
+                                                         int num_kv_heads, int page_size, int num_pages, float scale,
+                                                         int window, void* out, int skip_single, int max_q_len, int* status,
+                                                         int splits, float* scratch, int portion_tiles,
+                                                         const int* seq_of_token, float softcap, const float* slopes, const float* sinks,
+                                                         cudaStream_t stream) {
+  return shrike_paged_attention_tc_portions_kept(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, num_tokens,
+                                                 num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window, out,
+                                                 skip_single, max_q_len, status, splits, scratch, portion_tiles, seq_of_token,
+                                                 softcap, slopes, sinks, 0, stream);
 }
 
 SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void* q, const void* k_cache, const void* v_cache,
@@ -802,6 +831,12 @@ SHRIKE_API int shrike_paged_attention_tc_portions(const void*, const void*, cons
 SHRIKE_API int shrike_paged_attention_tc_portions_scores(const void*, const void*, const void*, const int*, int, const int*,
                                                          const int*, int, int, int, int, int, int, float, int, void*, int, int,
                                                          int*, int, float*, int, const int*, float, const float*, cudaStream_t) {
+  return SHRIKE_BAD_ARGUMENT;
+}
+SHRIKE_API int shrike_paged_attention_tc_portions_kept(const void*, const void*, const void*, const int*, int, const int*,
+                                                       const int*, int, int, int, int, int, int, float, int, void*, int, int,
+                                                       int*, int, float*, int, const int*, float, const float*, const float*,
+                                                       int, cudaStream_t) {
   return SHRIKE_BAD_ARGUMENT;
 }
 SHRIKE_API int shrike_paged_attention_tc_portions_sinks(const void*, const void*, const void*, const int*, int, const int*,

@@ -19,9 +19,12 @@
 //   head_rms         every head of a row over its root mean square, times one weight of the head's size.
 //
 // Sums, norms, gates, decays and states are float32; a result is rounded once, when it is stored in the activation type.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace streams {
+namespace cg = cooperative_groups;
 
 constexpr int MAX_STREAMS = 8;
 constexpr int MAX_TERMS = 4;
@@ -47,6 +50,7 @@ struct StreamNormArgs {
   float* sum_out;            // [rows][W] float32 or null: u itself
   const int* rows;           // null: every row, streams rewritten; else row r of the outputs is token rows[r]
   int n, width, count;
+  int split;                 // CTAs that share a row (a thread-block cluster along x): few rows are spread over the GPU
 };
 
 template <typename TO, int VEC>
@@ -67,12 +71,18 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a
   float* u_row = stream_shared;
   float* scratch = stream_shared + a.width;
   const int groups = a.width / VEC;
-  for (int row = blockIdx.x; row < a.n; row += gridDim.x) {
+  // A row's columns are dealt to the `split` CTAs of a cluster; their sums of squares meet through distributed shared
+  // memory, added in the order of the ranks by every CTA alike.
+  __shared__ float share;
+  const int split = a.split, rank = split > 1 ? static_cast<int>(blockIdx.x % split) : 0;
+  const int group_lo = static_cast<int>(static_cast<long long>(groups) * rank / split);
+  const int group_hi = static_cast<int>(static_cast<long long>(groups) * (rank + 1) / split);
+  for (int row = blockIdx.x / split; row < a.n; row += gridDim.x / split) {
     const int src = a.rows != nullptr ? a.rows[row] : row;
     float* x = a.x + static_cast<size_t>(src) * S * a.width;
     const size_t term_base = static_cast<size_t>(src) * a.width;
     float squares = 0.f;
-    for (int group = threadIdx.x; group < groups; group += blockDim.x) {
+    for (int group = group_lo + threadIdx.x; group < group_hi; group += blockDim.x) {
       const int col = group * VEC;
       float old[MAX_STREAMS][VEC];
 #pragma unroll
@@ -135,16 +145,25 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a
     }
     if (a.sum_out != nullptr) {
       __syncthreads();
-      for (int col = threadIdx.x; col < a.width; col += blockDim.x) a.sum_out[static_cast<size_t>(row) * a.width + col] = u_row[col];
+      for (int col = group_lo * VEC + threadIdx.x; col < group_hi * VEC; col += blockDim.x)
+        a.sum_out[static_cast<size_t>(row) * a.width + col] = u_row[col];
     }
     if (a.norm_w == nullptr || a.out == nullptr) {
       __syncthreads();
       continue;
     }
-    const float total = block_sum(squares, scratch);
+    float total = block_sum(squares, scratch);
+    if (split > 1) {
+      cg::cluster_group cluster = cg::this_cluster();
+      if (threadIdx.x == 0) share = total;
+      cluster.sync();
+      total = 0.f;
+      for (int other = 0; other < split; ++other) total += *cluster.map_shared_rank(&share, other);
+      cluster.sync();   // every CTA has read every share before one of them is written again or its CTA leaves
+    }
     const float r = rsqrtf(total / static_cast<float>(a.width) + a.eps);
     TO* out = static_cast<TO*>(a.out) + static_cast<size_t>(row) * a.width;
-    for (int group = threadIdx.x; group < groups; group += blockDim.x) {
+    for (int group = group_lo + threadIdx.x; group < group_hi; group += blockDim.x) {
       const int col = group * VEC;
       if constexpr (VEC == 4) {
         float w[4], v[4];
@@ -231,7 +250,7 @@ __global__ void __launch_bounds__(256) short_conv_keep_kernel(const ConvArgs a) 
 }
 
 // ------------------------------------------------------------------------------------------------ gated_scan
-constexpr int SCAN_TOKENS = 8;   // tokens staged at a time
+constexpr int SCAN_TOKENS = 16;   // tokens staged at a time: their loads are in flight together
 
 struct ScanArgs {
   const float* fused;     // [partials][N][total]: q (H D) | f (H D) | v (H Dv)
@@ -256,14 +275,14 @@ struct ScanArgs {
 __device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
 
 // One CTA owns `cols` value columns of one head's state for one sequence (or one run of its tokens) and walks the
-// tokens in order with the state in registers.  A column is shared by `lanes` neighbouring lanes of a warp (a power of
-// two, `row_groups` in the arguments): lane g of them holds rows g R .. g R + R - 1 of the column, so a token costs a
-// thread R multiply-adds for the state and R for its share of q . S, the shares meet by shuffles, and no barrier
-// falls inside the walk.  Tokens are staged SCAN_TOKENS at a time: q, f and 1 - f of the head (a lane's rows side by
-// side, each lane's run padded by four floats so that the lanes' 16-byte loads fall into different banks) and the
-// CTA's columns of v.
-template <int R>
-__global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
+// tokens in order with the state in registers.  C neighbouring columns are shared by `lanes` neighbouring lanes of a
+// warp (a power of two, `row_groups` in the arguments): lane g of them holds rows g R .. g R + R - 1 of those columns,
+// so a token costs a thread R C multiply-adds for the state and as many for its share of q . S, what it reads of q, f
+// and 1 - f serves C columns, the shares meet by shuffles, and no barrier falls inside the walk.  Tokens are staged
+// SCAN_TOKENS at a time: q, f and 1 - f of the head (a lane's rows side by side, each lane's run padded by four floats
+// so that the lanes' 16-byte loads fall into different banks) and the CTA's columns of v.
+template <int R, int C>
+__global__ void __launch_bounds__(128, R == 32 ? 2 : 4) gated_scan_kernel(const ScanArgs a) {
   extern __shared__ __align__(16) float scan_shared[];
   let_dependents_start();
   wait_for_previous();
@@ -277,7 +296,7 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
   float* decay = v + SCAN_TOKENS * cols;        // [D]: phase 1, the product of the run's gates
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane % lanes;
-  const int j = warp * (32 / lanes) + lane / lanes;     // this thread's column of the CTA's
+  const int j = (warp * (32 / lanes) + lane / lanes) * C;   // the first of this thread's columns among the CTA's
   const int head = blockIdx.y, col0 = blockIdx.x * cols;
   const int cols_here = min(cols, a.vdim - col0);
   int seq, first, length, run_index = -1;
@@ -297,20 +316,24 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
   const int slot = a.state_slot[seq];
   const bool held = slot >= 0 && slot < a.num_slots;
   const int HV = a.heads * a.vdim;
-  const bool mine = j < cols_here;
   if (!held) {   // a padding row: zeros out, nothing kept
-    if (a.phase != 1 && g == 0 && mine)
-      for (int t = 0; t < length; ++t) a.out[static_cast<size_t>(first + t) * HV + head * a.vdim + col0 + j] = 0.f;
+    if (a.phase != 1 && g == 0)
+      for (int t = 0; t < length; ++t)
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          if (j + c < cols_here) a.out[static_cast<size_t>(first + t) * HV + head * a.vdim + col0 + j + c] = 0.f;
     return;
   }
   float* slot_state = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.head_stride;
   float* run_state = a.run > 0 ? a.run_state + (static_cast<size_t>(run_index) * a.heads + head) * D * a.vdim : nullptr;
   const float* from = a.run == 0 ? slot_state : (a.phase == 3 ? run_state : nullptr);
-  float S[R];
+  float S[C][R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int d = g * R + r;
-    S[r] = from != nullptr && mine && d < D ? from[static_cast<size_t>(d) * a.vdim + col0 + j] : 0.f;
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+      S[c][r] = from != nullptr && j + c < cols_here && d < D ? from[static_cast<size_t>(d) * a.vdim + col0 + j + c] : 0.f;
   }
   // rows past the head's own (the lanes' runs cover lanes * R >= D of them) stay zero in q, f and 1 - f
   for (int i = threadIdx.x; i < 3 * SCAN_TOKENS * padded; i += blockDim.x) q[i] = 0.f;
@@ -320,6 +343,7 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
   for (int t0 = 0; t0 < length; t0 += SCAN_TOKENS) {
     const int here = min(SCAN_TOKENS, length - t0);
     __syncthreads();   // the tokens staged before are used up (and, the first time, the zeros are in place)
+#pragma unroll 8
     for (int i = threadIdx.x; i < here * D; i += blockDim.x) {
       const int t = i / D, d = i - t * D;
       const float* row = a.fused + static_cast<size_t>(first + t0 + t) * a.total;
@@ -334,6 +358,7 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
       f[at] = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
       k[at] = (1.0f - low) * sigmoid32(-zf);
     }
+#pragma unroll 8
     for (int i = threadIdx.x; i < here * cols; i += blockDim.x) {
       const int t = i / cols, c = i - t * cols;
       v[t * cols + c] = c < cols_here ? sum_partials(a.fused + static_cast<size_t>(first + t0 + t) * a.total + v_col + c, a.stride, a.partials) : 0.f;
@@ -346,46 +371,58 @@ __global__ void __launch_bounds__(256) gated_scan_kernel(const ScanArgs a) {
         decay[d] = p;
       }
     for (int t = 0; t < here; ++t) {
-      const float value = v[t * cols + j];
+      float value[C], partial[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        value[c] = v[t * cols + j + c];
+        partial[c] = 0.f;
+      }
       const float4* f4 = reinterpret_cast<const float4*>(f + t * padded + g * PITCH);
       const float4* k4 = reinterpret_cast<const float4*>(k + t * padded + g * PITCH);
       const float4* q4 = reinterpret_cast<const float4*>(q + t * padded + g * PITCH);
-      float partial = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const float4 ff = f4[r >> 2], kk = k4[r >> 2], qq = q4[r >> 2];
-        S[r] = __fmaf_rn(ff.x, S[r], kk.x * value);
-        S[r + 1] = __fmaf_rn(ff.y, S[r + 1], kk.y * value);
-        S[r + 2] = __fmaf_rn(ff.z, S[r + 2], kk.z * value);
-        S[r + 3] = __fmaf_rn(ff.w, S[r + 3], kk.w * value);
-        partial = __fmaf_rn(S[r], qq.x, partial);
-        partial = __fmaf_rn(S[r + 1], qq.y, partial);
-        partial = __fmaf_rn(S[r + 2], qq.z, partial);
-        partial = __fmaf_rn(S[r + 3], qq.w, partial);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          S[c][r] = __fmaf_rn(ff.x, S[c][r], kk.x * value[c]);
+          S[c][r + 1] = __fmaf_rn(ff.y, S[c][r + 1], kk.y * value[c]);
+          S[c][r + 2] = __fmaf_rn(ff.z, S[c][r + 2], kk.z * value[c]);
+          S[c][r + 3] = __fmaf_rn(ff.w, S[c][r + 3], kk.w * value[c]);
+          partial[c] = __fmaf_rn(S[c][r], qq.x, partial[c]);
+          partial[c] = __fmaf_rn(S[c][r + 1], qq.y, partial[c]);
+          partial[c] = __fmaf_rn(S[c][r + 2], qq.z, partial[c]);
+          partial[c] = __fmaf_rn(S[c][r + 3], qq.w, partial[c]);
+        }
       }
       if (a.phase == 1) continue;   // a run's own addition to the state: its outputs come in phase 3
-      for (int offset = lanes >> 1; offset > 0; offset >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, offset);
-      if (g == 0 && mine) a.out[static_cast<size_t>(first + t0 + t) * HV + head * a.vdim + col0 + j] = partial;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        for (int offset = lanes >> 1; offset > 0; offset >>= 1) partial[c] += __shfl_xor_sync(0xffffffffu, partial[c], offset);
+        if (g == 0 && j + c < cols_here) a.out[static_cast<size_t>(first + t0 + t) * HV + head * a.vdim + col0 + j + c] = partial[c];
+      }
     }
   }
   if (a.phase == 1) {
-    if (mine) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int d = g * R + r;
-        if (d < D) run_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[r];
-      }
+    for (int r = 0; r < R; ++r) {
+      const int d = g * R + r;
+#pragma unroll
+      for (int c = 0; c < C; ++c)
+        if (d < D && j + c < cols_here) run_state[static_cast<size_t>(d) * a.vdim + col0 + j + c] = S[c][r];
     }
     __syncthreads();
     if (blockIdx.x == 0)
       for (int d = threadIdx.x; d < D; d += blockDim.x) a.run_decay[(static_cast<size_t>(run_index) * a.heads + head) * D + d] = decay[d];
     return;
   }
-  if (a.run == 0 && mine) {
+  if (a.run == 0) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int d = g * R + r;
-      if (d < D) slot_state[static_cast<size_t>(d) * a.vdim + col0 + j] = S[r];
+#pragma unroll
+      for (int c = 0; c < C; ++c)
+        if (d < D && j + c < cols_here) slot_state[static_cast<size_t>(d) * a.vdim + col0 + j + c] = S[c][r];
     }
   }
 }
@@ -417,12 +454,23 @@ __global__ void __launch_bounds__(256) gated_scan_carry_kernel(const ScanArgs a)
   const int d = element / a.vdim;
   float* slot_state = a.state + (static_cast<size_t>(slot) * a.heads + head) * a.head_stride + element;
   float s = *slot_state;
-  for (int run = a.run_first[seq]; run < a.run_first[seq + 1]; ++run) {
-    float* own = a.run_state + (static_cast<size_t>(run) * a.heads + head) * size + element;
-    const float added = *own;
-    const float p = a.run_decay[(static_cast<size_t>(run) * a.heads + head) * a.dim + d];
-    *own = s;
-    s = __fmaf_rn(p, s, added);
+  const int last = a.run_first[seq + 1];
+  // eight runs' additions and decays are asked for together: the walk is one memory latency per eight runs
+  for (int run0 = a.run_first[seq]; run0 < last; run0 += 8) {
+    float added[8], p[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const size_t at = static_cast<size_t>(min(run0 + i, last - 1)) * a.heads + head;
+      added[i] = a.run_state[at * size + element];
+      p[i] = a.run_decay[at * a.dim + d];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (run0 + i < last) {
+        a.run_state[(static_cast<size_t>(run0 + i) * a.heads + head) * size + element] = s;
+        s = __fmaf_rn(p[i], s, added[i]);
+      }
+    }
   }
   *slot_state = s;
 }
@@ -470,16 +518,22 @@ SHRIKE_API int shrike_stream_norm(float* x, const float* const* data, const int*
   }
   a.mix = mix; a.out_w = out_w; a.layer_scale = layer_scale; a.in_w = in_w; a.norm_w = norm_w; a.eps = eps;
   a.out = out; a.sum_out = sum_out; a.rows = rows; a.n = n; a.width = width; a.count = count;
+  // few rows (a decode step, the final norm's wanted rows): a row's columns go to the CTAs of a cluster, as many as
+  // leave every CTA a few hundred columns
+  a.split = 1;
+  if (n <= 64 && norm_w != nullptr && out != nullptr)
+    while (a.split < 8 && width / (vec ? 4 : 1) / (a.split * 2) >= 64) a.split *= 2;
   const size_t smem = (static_cast<size_t>(width) + 33) * sizeof(float);
   if (smem > static_cast<size_t>(shrike_device().max_smem)) return SHRIKE_BAD_ARGUMENT;
   const bool bf16 = out != nullptr && out_dtype == SHRIKE_BF16;
   if (out != nullptr && out_dtype != SHRIKE_BF16 && out_dtype != SHRIKE_F32) return SHRIKE_BAD_ARGUMENT;
-  const unsigned grid = static_cast<unsigned>(n);
+  const unsigned grid = static_cast<unsigned>(n) * static_cast<unsigned>(a.split);
 #define SHRIKE_STREAM_CASE(T, V)                                                                                        \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
       cudaFuncSetAttribute(stream_norm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    launch_dependent(stream_norm_kernel<T, V>, grid, 256, smem, stream, a);                                             \
+    if (a.split > 1) launch_dependent_clusters(stream_norm_kernel<T, V>, grid, 256, smem, stream, a.split, a);          \
+    else launch_dependent(stream_norm_kernel<T, V>, grid, 256, smem, stream, a);                                        \
   } while (0)
   if (bf16 && vec) SHRIKE_STREAM_CASE(__nv_bfloat16, 4);
   else if (bf16) SHRIKE_STREAM_CASE(__nv_bfloat16, 1);
@@ -508,17 +562,18 @@ SHRIKE_API int shrike_short_conv(const float* fused, int partials, long long str
   return shrike_launch_status();
 }
 
-// How the scan is laid out for heads of dim x vdim: R rows of a column a thread (32, or 8 for small heads), the
-// lanes that share a column (a power of two covering dim), the columns a CTA of up to eight warps takes.
-struct ScanShape { int rows, lanes, cols, threads; size_t smem; };
+// How the scan is laid out for heads of dim x vdim: R rows of C neighbouring columns a thread (8 x 4 for heads of up
+// to 32 rows, 16 x 4 up to 512, 32 x 2 up to 1,024), the lanes that share those columns (a power of two covering
+// dim), the columns a CTA of up to four warps takes.
+struct ScanShape { int rows, each, lanes, cols, threads; size_t smem; };
 static inline bool scan_shape(int dim, int vdim, ScanShape* shape) {
-  const int rows = dim >= 64 ? 32 : 8;
+  const int rows = dim <= 32 ? 8 : (dim <= 512 ? 16 : 32), each = rows == 32 ? 2 : 4;
   int lanes = 1;
   while (lanes * rows < dim) lanes *= 2;
   if (lanes > 32) return false;
-  const int per_warp = 32 / lanes;
-  const int warps = max(1, min(8, (vdim + per_warp - 1) / per_warp));
-  shape->rows = rows; shape->lanes = lanes; shape->cols = per_warp * warps; shape->threads = warps * 32;
+  const int per_warp = 32 / lanes * each;
+  const int warps = max(1, min(4, (vdim + per_warp - 1) / per_warp));
+  shape->rows = rows; shape->each = each; shape->lanes = lanes; shape->cols = per_warp * warps; shape->threads = warps * 32;
   shape->smem = (static_cast<size_t>(3) * SCAN_TOKENS * lanes * (rows + 4) + static_cast<size_t>(SCAN_TOKENS) * shape->cols + dim) * sizeof(float);
   return shape->smem <= static_cast<size_t>(shrike_device().max_smem);
 }
@@ -542,7 +597,7 @@ SHRIKE_API int shrike_gated_scan(const float* fused, int partials, long long str
   if (!scan_shape(dim, vdim, &shape)) return SHRIKE_BAD_ARGUMENT;   // heads of more than 1,024 rows
   ScanArgs a = {fused, stride, partials, total, f_bias, lower, state, q_start, state_slot, out, heads, dim, vdim,
                 head_stride, shape.cols, shape.lanes, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs};
-  void (*kernel)(ScanArgs) = shape.rows == 32 ? gated_scan_kernel<32> : gated_scan_kernel<8>;
+  void (*kernel)(ScanArgs) = shape.rows == 32 ? gated_scan_kernel<32, 2> : (shape.rows == 16 ? gated_scan_kernel<16, 4> : gated_scan_kernel<8, 4>);
   if (shape.smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shape.smem));
   const unsigned slices = static_cast<unsigned>((vdim + shape.cols - 1) / shape.cols);
   const unsigned threads = static_cast<unsigned>(shape.threads);

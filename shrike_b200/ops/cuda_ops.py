@@ -246,6 +246,10 @@ class CudaOps:
             [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P, _P]
         )
         lib.shrike_paged_attention_tc_portions_sinks.restype = _I
+        lib.shrike_paged_attention_tc_portions_kept.argtypes = (
+            [_P, _P, _P, _P, _I, _P, _P] + [_I] * 6 + [_F, _I, _P, _I, _I, _P, _I, _P, _I, _P, _F, _P, _P, _I, _P]
+        )
+        lib.shrike_paged_attention_tc_portions_kept.restype = _I
         lib.shrike_attention_tc_portions_rows.restype = _I
         lib.shrike_attention_tc_portions_splits.argtypes = [_I, _I, _I, _I, _I]
         lib.shrike_attention_tc_portions_splits.restype = _I
@@ -575,18 +579,16 @@ class CudaOps:
             if slopes.numel() != num_heads:
                 raise KernelError("one distance slope per query head")
         plan = self.attention_plan(num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                                   q.shape[0], q_lens)
-        # kept first keys: the tcgen05 portions kernel walks one run of tiles, so such layers' portions take the mma.sync one
-        tc_portions = plan.tc_portions and not keep_first
-        self.launches += plan.has_single + plan.has_portions + (1 if tc_portions and plan.portion_splits > 1 else 0)
+                                   q.shape[0], q_lens, keep_first=keep_first)
+        self.launches += plan.has_single + plan.has_portions + (1 if plan.portion_splits > 1 else 0)
         has_portions = plan.has_portions
-        if tc_portions:
-            _check(lib.shrike_paged_attention_tc_portions_sinks(
+        if plan.tc_portions:
+            _check(lib.shrike_paged_attention_tc_portions_kept(
                 _ptr(q), _ptr(keys), _ptr(values), _ptr(block_table), max_blocks, _ptr(q_start), _ptr(ctx_len),
                 q.shape[0], num_seqs, num_heads, num_kv_heads, page_size, num_pages, scale, window or 0, _ptr(out),
                 plan.has_single, max_q_len, _ptr(self.status), plan.portion_splits, _ptr(plan.portion_scratch),
                 self.portion_tiles(q_lens, plan.has_single, lib.shrike_attention_tc_portions_rows()), _ptr(seq_of_token),
-                softcap or 0.0, _ptr(slopes), _ptr(sinks), self._stream()), "paged_attention_tc_portions")
+                softcap or 0.0, _ptr(slopes), _ptr(sinks), keep_first, self._stream()), "paged_attention_tc_portions")
             has_portions = 0
             if not plan.has_single:
                 return
@@ -609,7 +611,7 @@ class CudaOps:
         return tiles
 
     def attention_plan(self, num_heads, num_kv_heads, head_dim, num_seqs, max_blocks, page_size, max_q_len, min_q_len,
-                       num_tokens=0, q_lens=None):
+                       num_tokens=0, q_lens=None, keep_first=0):
         """How a bfloat16 batch's attention is cut: which kernels run (single tokens, portions, the
         tensor-core form of the latter), the key splits and clusters of the single-token kernel, the
         key splits of the portions kernel, and their scratch.  A function of the batch's shape alone."""
@@ -640,10 +642,12 @@ class CudaOps:
             tiles = self.portion_tiles(q_lens, has_single, lib.shrike_attention_tc_portions_rows())
             portion_splits = self.portion_splits or lib.shrike_attention_tc_portions_splits(
                 num_tokens, num_heads, max_blocks, page_size, tiles)
-            need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits)
+            kept = 1 if keep_first else 0   # kept first keys are one more split of their own, behind the window's
+            need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits + kept)
             if need > self.PORTION_SCRATCH_FLOATS:   # bound the scratch: fewer splits, never a refusal
-                portion_splits = max(1, portion_splits * self.PORTION_SCRATCH_FLOATS // need)
-                need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits)
+                portion_splits = max(1, (portion_splits + kept) * self.PORTION_SCRATCH_FLOATS // need - kept)
+                need = lib.shrike_attention_tc_portions_scratch_floats(num_tokens, num_heads, portion_splits + kept)
+            portion_splits += kept
             if portion_splits > 1:
                 if self._portion_scratch is None or self._portion_scratch.numel() < need:
                     self._portion_scratch = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=self.device)
