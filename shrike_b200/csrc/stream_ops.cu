@@ -53,8 +53,9 @@ struct StreamNormArgs {
   int split;                 // CTAs that share a row (a thread-block cluster along x): few rows are spread over the GPU
 };
 
-template <typename TO, int VEC>
-__global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a) {
+// MAXS: the most streams an instance holds in registers (1, 2, 4 or 8): fewer registers, more rows under way an SM
+template <typename TO, int VEC, int MAXS>
+__global__ void __launch_bounds__(256, MAXS <= 4 ? 3 : 2) stream_norm_kernel(const StreamNormArgs a) {
   extern __shared__ float stream_shared[];   // [width] u, then 33 floats for the block's sum
   __shared__ float mix[MAX_STREAMS * MAX_STREAMS], out_w[MAX_STREAMS], in_w[MAX_STREAMS];
   let_dependents_start();
@@ -84,9 +85,9 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a
     float squares = 0.f;
     for (int group = group_lo + threadIdx.x; group < group_hi; group += blockDim.x) {
       const int col = group * VEC;
-      float old[MAX_STREAMS][VEC];
+      float old[MAXS][VEC];
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s) {
+      for (int s = 0; s < MAXS; ++s) {
         if (s < S) {
           if constexpr (VEC == 4) load4<float>(x + static_cast<size_t>(s) * a.width + col, old[s]);
           else old[s][0] = x[static_cast<size_t>(s) * a.width + col];
@@ -113,14 +114,14 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(const StreamNormArgs a
 #pragma unroll
       for (int e = 0; e < VEC; ++e) u[e] = 0.f;
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) {
+      for (int t = 0; t < MAXS; ++t) {
         if (t < S) {
           float fresh[VEC];
           if (pending) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) fresh[e] = __fmul_rn(out_w[t], y[e]);
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; ++s)
+            for (int s = 0; s < MAXS; ++s)
               if (s < S) {
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) fresh[e] = __fmaf_rn(mix[s * S + t], old[s][e], fresh[e]);
@@ -270,9 +271,19 @@ struct ScanArgs {
   float* run_decay;       // [runs][H][D]: the product of a run's forget gates
   int* run_first;         // [S + 1]: index of each sequence's first run; last, the number of runs
   int num_seqs;
+  int fast_math;          // 1: the hardware exponential and reciprocal in the gates (a bfloat16 engine)
 };
 
-__device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf(-z)); }
+// sigmoid(z) and sigmoid(-z) = 1 - sigmoid(z) from one exponential of -|z| and one reciprocal: neither is formed as a
+// difference, so the smaller of the two keeps its digits.  `fast`: the hardware exponential and reciprocal (relative
+// error about 2^-21; the bfloat16 engine, whose results keep 8 bits).
+__device__ __forceinline__ void sigmoid_both(float z, bool fast, float& with, float& against) {
+  const float e = fast ? __expf(-fabsf(z)) : expf(-fabsf(z));             // in (0, 1]
+  const float larger = fast ? __fdividef(1.0f, 1.0f + e) : 1.0f / (1.0f + e);   // sigmoid(|z|)
+  const float smaller = e * larger;                                       // sigmoid(-|z|)
+  with = z >= 0.f ? larger : smaller;
+  against = z >= 0.f ? smaller : larger;
+}
 
 // One CTA owns `cols` value columns of one head's state for one sequence (or one run of its tokens) and walks the
 // tokens in order with the state in registers.  C neighbouring columns are shared by `lanes` neighbouring lanes of a
@@ -282,7 +293,7 @@ __device__ __forceinline__ float sigmoid32(float z) { return 1.0f / (1.0f + expf
 // SCAN_TOKENS at a time: q, f and 1 - f of the head (a lane's rows side by side, each lane's run padded by four floats
 // so that the lanes' 16-byte loads fall into different banks) and the CTA's columns of v.
 template <int R, int C>
-__global__ void __launch_bounds__(128, R == 32 ? 2 : 4) gated_scan_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(C == 1 ? 256 : 128, C == 1 || (R == 32 && C == 2) ? 2 : 4) gated_scan_kernel(const ScanArgs a) {
   extern __shared__ __align__(16) float scan_shared[];
   let_dependents_start();
   wait_for_previous();
@@ -335,8 +346,15 @@ __global__ void __launch_bounds__(128, R == 32 ? 2 : 4) gated_scan_kernel(const 
     for (int c = 0; c < C; ++c)
       S[c][r] = from != nullptr && j + c < cols_here && d < D ? from[static_cast<size_t>(d) * a.vdim + col0 + j + c] : 0.f;
   }
-  // rows past the head's own (the lanes' runs cover lanes * R >= D of them) stay zero in q, f and 1 - f
-  for (int i = threadIdx.x; i < 3 * SCAN_TOKENS * padded; i += blockDim.x) q[i] = 0.f;
+  // rows past the head's own (the lanes' runs cover lanes * R >= D of them) are zero in q, f and 1 - f, so that the
+  // state's rows there stay zero; the four floats between two lanes' runs are never read
+  for (int i = threadIdx.x; i < SCAN_TOKENS * (lanes * R - D); i += blockDim.x) {
+    const int t = i / (lanes * R - D), d = D + i % (lanes * R - D);
+    const int at = t * padded + (d / R) * PITCH + d % R;
+    q[at] = 0.f;
+    f[at] = 0.f;
+    k[at] = 0.f;
+  }
   if (a.phase == 1)
     for (int d = threadIdx.x; d < D; d += blockDim.x) decay[d] = 1.f;
   const int q_col = head * D, f_col = a.heads * D + head * D, v_col = 2 * a.heads * D + head * a.vdim + col0;
@@ -354,9 +372,12 @@ __global__ void __launch_bounds__(128, R == 32 ? 2 : 4) gated_scan_kernel(const 
       const int at = t * padded + (d / R) * PITCH + d % R;
       // 1 - f = (1 - lower) (1 - sigmoid(z)) = (1 - lower) sigmoid(-z): formed so, a gate close to one keeps the
       // digits of what it lets in, which 1 - f computed from f would lose
-      q[at] = zq * sigmoid32(zq);
-      f[at] = __fmaf_rn(1.0f - low, sigmoid32(zf), low);
-      k[at] = (1.0f - low) * sigmoid32(-zf);
+      float open, shut, q_gate, unused;
+      sigmoid_both(zf, a.fast_math != 0, open, shut);
+      sigmoid_both(zq, a.fast_math != 0, q_gate, unused);
+      q[at] = zq * q_gate;
+      f[at] = __fmaf_rn(1.0f - low, open, low);
+      k[at] = (1.0f - low) * shut;
     }
 #pragma unroll 8
     for (int i = threadIdx.x; i < here * cols; i += blockDim.x) {
@@ -528,17 +549,25 @@ SHRIKE_API int shrike_stream_norm(float* x, const float* const* data, const int*
   const bool bf16 = out != nullptr && out_dtype == SHRIKE_BF16;
   if (out != nullptr && out_dtype != SHRIKE_BF16 && out_dtype != SHRIKE_F32) return SHRIKE_BAD_ARGUMENT;
   const unsigned grid = static_cast<unsigned>(n) * static_cast<unsigned>(a.split);
-#define SHRIKE_STREAM_CASE(T, V)                                                                                        \
+#define SHRIKE_STREAM_LAUNCH(T, V, M)                                                                                   \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
-      cudaFuncSetAttribute(stream_norm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    if (a.split > 1) launch_dependent_clusters(stream_norm_kernel<T, V>, grid, 256, smem, stream, a.split, a);          \
-    else launch_dependent(stream_norm_kernel<T, V>, grid, 256, smem, stream, a);                                        \
+      cudaFuncSetAttribute(stream_norm_kernel<T, V, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    if (a.split > 1) launch_dependent_clusters(stream_norm_kernel<T, V, M>, grid, 256, smem, stream, a.split, a);       \
+    else launch_dependent(stream_norm_kernel<T, V, M>, grid, 256, smem, stream, a);                                     \
+  } while (0)
+#define SHRIKE_STREAM_CASE(T, V)                                                                                        \
+  do {                                                                                                                  \
+    if (count <= 1) SHRIKE_STREAM_LAUNCH(T, V, 1);                                                                      \
+    else if (count <= 2) SHRIKE_STREAM_LAUNCH(T, V, 2);                                                                 \
+    else if (count <= 4) SHRIKE_STREAM_LAUNCH(T, V, 4);                                                                 \
+    else SHRIKE_STREAM_LAUNCH(T, V, 8);                                                                                 \
   } while (0)
   if (bf16 && vec) SHRIKE_STREAM_CASE(__nv_bfloat16, 4);
   else if (bf16) SHRIKE_STREAM_CASE(__nv_bfloat16, 1);
   else if (vec) SHRIKE_STREAM_CASE(float, 4);
   else SHRIKE_STREAM_CASE(float, 1);
+#undef SHRIKE_STREAM_LAUNCH
 #undef SHRIKE_STREAM_CASE
   return shrike_launch_status();
 }
@@ -562,17 +591,22 @@ SHRIKE_API int shrike_short_conv(const float* fused, int partials, long long str
   return shrike_launch_status();
 }
 
-// How the scan is laid out for heads of dim x vdim: R rows of C neighbouring columns a thread (8 x 4 for heads of up
-// to 32 rows, 16 x 4 up to 512, 32 x 2 up to 1,024), the lanes that share those columns (a power of two covering
-// dim), the columns a CTA of up to four warps takes.
+// How the scan is laid out for heads of dim x vdim: R rows of C neighbouring columns a thread, the lanes that share
+// those columns (a power of two covering dim), the columns a CTA of up to four warps takes.  `wide` (16 x 4; 8 x 4 for
+// heads of up to 32 rows, 32 x 2 above 512): what a thread reads of q, f and 1 - f serves four columns, which is what
+// bounds a walk when there is enough of it to fill the GPU; otherwise one column a thread (32 x 1, 8 x 1), twice to four
+// times the threads for the same state.
 struct ScanShape { int rows, each, lanes, cols, threads; size_t smem; };
-static inline bool scan_shape(int dim, int vdim, ScanShape* shape) {
-  const int rows = dim <= 32 ? 8 : (dim <= 512 ? 16 : 32), each = rows == 32 ? 2 : 4;
+static inline bool scan_shape(int dim, int vdim, bool wide, ScanShape* shape) {
+  int rows, each;
+  if (dim <= 32) { rows = 8; each = wide ? 4 : 1; }
+  else if (dim <= 512 && wide) { rows = 16; each = 4; }
+  else { rows = 32; each = wide ? 2 : 1; }
   int lanes = 1;
   while (lanes * rows < dim) lanes *= 2;
   if (lanes > 32) return false;
   const int per_warp = 32 / lanes * each;
-  const int warps = max(1, min(4, (vdim + per_warp - 1) / per_warp));
+  const int warps = max(1, min(each == 1 ? 8 : 4, (vdim + per_warp - 1) / per_warp));   // either way up to 64 columns a CTA at 128 rows
   shape->rows = rows; shape->each = each; shape->lanes = lanes; shape->cols = per_warp * warps; shape->threads = warps * 32;
   shape->smem = (static_cast<size_t>(3) * SCAN_TOKENS * lanes * (rows + 4) + static_cast<size_t>(SCAN_TOKENS) * shape->cols + dim) * sizeof(float);
   return shape->smem <= static_cast<size_t>(shrike_device().max_smem);
@@ -587,21 +621,28 @@ SHRIKE_API long long shrike_gated_scan_runs(int n, int num_seqs, int run) { retu
 SHRIKE_API int shrike_gated_scan(const float* fused, int partials, long long stride, int total, const float* f_bias,
                                  const float* lower, float* state, const int* q_start, const int* state_slot, float* out,
                                  int num_seqs, int heads, int dim, int vdim, int head_stride, int num_slots, int run,
-                                 float* run_state, float* run_decay, int* run_first, int num_runs,
+                                 float* run_state, float* run_decay, int* run_first, int num_runs, int fast_math,
                                  cudaStream_t stream) {
   if (num_seqs <= 0) return SHRIKE_OK;
   if (heads < 1 || heads > 65535 || num_seqs > 65535 || dim < 1 || vdim < 1 || partials < 1 || head_stride < dim * vdim ||
       total < heads * (2 * dim + vdim))
     return SHRIKE_BAD_ARGUMENT;
+  // the wide form where the walks fill the GPU with it (about three warps a sub-partition), else one column a thread
+  const bool runs = run > 0 && run_state != nullptr && run_decay != nullptr && run_first != nullptr && num_runs >= 1;
   ScanShape shape;
-  if (!scan_shape(dim, vdim, &shape)) return SHRIKE_BAD_ARGUMENT;   // heads of more than 1,024 rows
+  if (!scan_shape(dim, vdim, true, &shape)) return SHRIKE_BAD_ARGUMENT;   // heads of more than 1,024 rows
+  const long long wide_threads = static_cast<long long>(heads) * (runs ? num_runs : num_seqs) * ((vdim + shape.each - 1) / shape.each) * shape.lanes;
+  if (wide_threads < static_cast<long long>(shrike_device().sm_count) * 384 && !scan_shape(dim, vdim, false, &shape)) return SHRIKE_BAD_ARGUMENT;
   ScanArgs a = {fused, stride, partials, total, f_bias, lower, state, q_start, state_slot, out, heads, dim, vdim,
-                head_stride, shape.cols, shape.lanes, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs};
-  void (*kernel)(ScanArgs) = shape.rows == 32 ? gated_scan_kernel<32, 2> : (shape.rows == 16 ? gated_scan_kernel<16, 4> : gated_scan_kernel<8, 4>);
+                head_stride, shape.cols, shape.lanes, num_slots, 0, 0, nullptr, nullptr, nullptr, num_seqs, fast_math};
+  void (*kernel)(ScanArgs) = nullptr;
+  if (shape.rows == 8) kernel = shape.each == 4 ? gated_scan_kernel<8, 4> : gated_scan_kernel<8, 1>;
+  else if (shape.rows == 16) kernel = gated_scan_kernel<16, 4>;
+  else kernel = shape.each == 2 ? gated_scan_kernel<32, 2> : gated_scan_kernel<32, 1>;
   if (shape.smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shape.smem));
   const unsigned slices = static_cast<unsigned>((vdim + shape.cols - 1) / shape.cols);
   const unsigned threads = static_cast<unsigned>(shape.threads);
-  if (run <= 0 || run_state == nullptr || run_decay == nullptr || run_first == nullptr || num_runs < 1) {
+  if (!runs) {
     launch_dependent(kernel, dim3(slices, heads, num_seqs), threads, shape.smem, stream, a);
     return shrike_launch_status();
   }

@@ -169,7 +169,7 @@ class CudaOps:
         lib.shrike_concat_cast.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P]
         lib.shrike_stream_norm.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _P]
         lib.shrike_short_conv.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P, _P] + [_I] * 5 + [_P]
-        lib.shrike_gated_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 7 + [_P, _P, _P, _I, _P]
+        lib.shrike_gated_scan.argtypes = [_P, _I, _LL, _I, _P, _P, _P, _P, _P, _P] + [_I] * 7 + [_P, _P, _P, _I, _I, _P]
         lib.shrike_gated_scan_runs.argtypes = [_I, _I, _I]
         lib.shrike_gated_scan_runs.restype = _LL
         lib.shrike_head_rms.argtypes = [_P, _P, _P, _I, _I, _I, _I, _F, _P]
@@ -1050,7 +1050,7 @@ class CudaOps:
         _check(self.core.shrike_gated_scan(
             _ptr(fused), partials, stride, fused.shape[-1], _ptr(f_bias), _ptr(lower), _ptr(state), _ptr(q_start), _ptr(state_slot),
             _ptr(out), num_seqs, num_heads, dim, vdim, state.shape[-1], state.shape[0], run, _ptr(run_state), _ptr(run_decay),
-            _ptr(run_first), runs, self._stream()), "gated_scan")
+            _ptr(run_first), runs, int(self.dtype == torch.bfloat16), self._stream()), "gated_scan")
 
     def head_rms(self, x, weight, eps, out, heads):
         """out[n, h, :] = x[n, h, :] / sqrt(mean(x[n, h, :]^2) + eps) * weight for x float32 [N, heads * size]."""
