@@ -973,8 +973,10 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
   const float shared_dot = rows > experts ? score[experts] : 0.f;
   float total = 0.f;
   for (int e = lane; e < experts; e += 32) {
-    // an expert's score: its share of the softmax over all experts, or the sigmoid of its own logit
-    const float p = sigmoid_scores ? 1.0f / (1.0f + expf(-score[e])) : expf(score[e] - best);
+    // an expert's score: its share of the softmax over all experts, or the sigmoid of its own logit.  The sigmoid is
+    // taken when an expert is chosen: the choice itself goes by the logits, which order the experts as their sigmoids
+    // do and do not run together where the sigmoid rounds to 1 or to 0
+    const float p = sigmoid_scores ? score[e] : expf(score[e] - best);
     score[e] = p;
     total += p;
   }
@@ -986,9 +988,10 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
   }
   __syncwarp();
   float chosen_sum = 0.f;
-  // `top` rounds of a warp-wide argmax; the lowest index wins a tie.  A pick is marked by a negative score.
+  // `top` rounds of a warp-wide argmax; the lowest index wins a tie.  A pick is marked by a value below every score.
+  const float below = sigmoid_scores ? -INFINITY : -1.f;
   for (int round = 0; round < top; ++round) {
-    float mine = -1.f;
+    float mine = below;
     int where = experts;
     for (int e = lane; e < experts; e += 32)
       if (score[e] > mine) { mine = score[e]; where = e; }
@@ -998,10 +1001,11 @@ route_top_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
       const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
       if (other > mine || (other == mine && other_where < where)) { mine = other; where = other_where; }
     }
+    if (sigmoid_scores) mine = 1.0f / (1.0f + expf(-mine));
     chosen_sum += mine;
     if (lane == 0 && where < experts) {
       out[where] = mine;
-      score[where] = -2.f;
+      score[where] = sigmoid_scores ? -INFINITY : -2.f;
     }
     __syncwarp();
   }

@@ -131,7 +131,8 @@ class EmulatedOps:
     def route_top(self, x, router, shared_gate, weights, top, renorm_eps, scoring="softmax", renormalise=True):
         logits = x.float() @ router.T
         scores = torch.sigmoid(logits) if scoring == "sigmoid" else torch.softmax(logits, -1)
-        best, chosen = torch.topk(scores, top, -1)
+        _, chosen = torch.topk(logits, top, -1)   # the logits order the experts as either score does
+        best = scores.gather(1, chosen)
         weights.zero_()
         weights[:, : router.shape[0]].scatter_(1, chosen, best / (best.sum(-1, keepdim=True) + renorm_eps) if renormalise else best)
         if weights.shape[1] > router.shape[0]:

@@ -93,7 +93,30 @@ SETOTAR = {
         _with(_attention(2, 1, 16, 16, 0.25, {"dims": 16, "base": 100.0}), experts=2, top=1, ff=8),
     ]},
 }
-SETOTAR_SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44, "E": 45}
+SETOTAR_SEEDS = {"A": 41, "B": 42, "C": 43, "D": 44, "E": 45, "M": 46, "N": 47}
+
+_STRETCH_M = {"dims": 32, "base": 10000.0, "scaling": _yarn(4.0, 256, 16.0, 1.0)}
+_STRETCH_N = {"dims": 32, "base": 30000.0, "scaling": _yarn(6.0, 1024, 16.0, 2.0)}
+# heads of 64 and 128, the sizes the tcgen05 kernels serve, at widths of a few hundred: prompts of several hundred
+# tokens run through those kernels, the kept keys' split, the runs of the recurrence and the clusters of the norm
+MEDIUM = {
+    "M": {"architecture": "Setotar", "width": 320, "vocab": 1000, "norm": {"eps": 1e-6}, "streams": 3, "layers": [
+        _with(_attention(5, 5, 64, 64, 0.125, _STRETCH_M), experts=4, top=2, ff=96),
+        _with(_parallel(_left(6, 2, 64, 64, 0.125, {"dims": 64, "base": 5000.0, "scaling": {"factor": 2.0}}, conv=3, size=200, keep=7, softcap=15.0),
+                        (2, 64, 32), (1.1, 0.8)), experts=6, top=1, ff=48),
+        _with(_attention(5, 5, 64, 64, 0.125, _STRETCH_M, kv_from=0)),
+        _with(_parallel(_left(2, 2, 128, 128, 0.09, {"dims": 32, "base": 100.0}, conv=5, size=64, keep=33), (3, 32, 96), (0.5, 1.5)), experts=3, top=3, ff=64),
+        _with(_attention(3, 1, 128, 64, 0.1, {"dims": 128, "base": 300.0}), experts=2, top=1, ff=200),
+    ]},
+    "N": {"architecture": "Setotar", "width": 192, "vocab": 777, "norm": {"eps": 1e-5}, "streams": 2, "layers": [
+        _with(_parallel(_left(8, 2, 128, 48, 0.09, {"dims": 64, "base": 30000.0, "scaling": {"factor": 6.0}}, conv=6, size=150, keep=6, softcap=25.0),
+                        (4, 48, 64), (1.3, 0.7)), experts=8, top=1, ff=64),
+        _with(_parallel(_left(4, 4, 64, 128, 0.12, None, conv=2, size=300, keep=0, softcap=50.0), (1, 200, 40), (1.0, 1.0)), experts=8, top=3, ff=40),
+        _with(_attention(4, 2, 64, 64, 0.19, _STRETCH_N), experts=5, top=1, ff=64),
+        _with(_attention(4, 2, 64, 64, 0.19, _STRETCH_N, kv_from=2), experts=5, top=1, ff=64),
+    ]},
+}
+SETOTAR.update(MEDIUM)
 
 
 def sharpened(tensors: dict) -> dict:

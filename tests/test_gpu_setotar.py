@@ -22,7 +22,7 @@ from tests.setotar_configs import ASKER, MARK, SETOTAR, make_setotar_folder, pla
 
 pytestmark = pytest.mark.gpu
 LENGTHS = {"A": [5, 47, 1, 230, 2, 64, 33], "B": [5, 17, 150, 70, 1, 90, 2], "C": [40, 3, 25, 1, 18], "D": [30, 2, 300, 140],
-           "E": [9, 100, 1, 33]}
+           "E": [9, 100, 1, 33], "M": [700, 37, 1, 260, 5], "N": [700, 37, 1, 260, 5]}
 _cache = {}
 
 
@@ -105,6 +105,20 @@ WAYS = {
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("key,page", [("A", 16), ("B", 16), ("A", 8), ("B", 24), ("C", 4), ("C", 32), ("D", 16), ("D", 64), ("E", 16)])
 def test_replay_matches_plain(tmp_path_factory, key, page, dtype, way):
+    folder, requests, want, scale, limits, margins = reference(key, dtype, tmp_path_factory)
+    steps = WAYS[way](requests)
+    got, session = replay(folder, dtype, steps, poison=way.startswith("mixed"), page_size=page, max_live=4)
+    assert session.runner.cache.whole(), "pages or slots were not given back"
+    for ident in requests:
+        check(got[ident], want[ident], scale, limits[ident], f"{key} page {page} {dtype} {way} {ident}", margins[ident])
+
+
+@pytest.mark.parametrize("way", ["whole", "tail", "long_portions", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key,page", [("M", 16), ("N", 32)])
+def test_heads_of_the_tensor_core_kernels_sizes_and_long_prompts(tmp_path_factory, key, page, dtype, way):
+    """Heads of 64 and 128 with prompts of several hundred tokens: the tcgen05 portions kernel with the kept keys' split,
+    the recurrence's runs, the norm's clusters, the paged single-token kernel."""
     folder, requests, want, scale, limits, margins = reference(key, dtype, tmp_path_factory)
     steps = WAYS[way](requests)
     got, session = replay(folder, dtype, steps, poison=way.startswith("mixed"), page_size=page, max_live=4)
@@ -256,7 +270,7 @@ def sequence_with(count, place, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window,keep,page", [(1, 1, 16), (2, 5, 16), (17, 4, 16), (32, 16, 16), (136, 4, 16), (21, 9, 8), (64, 70, 64), (300, 3, 32)])
+@pytest.mark.parametrize("window,keep,page", [(1, 1, 16), (2, 5, 16), (17, 4, 16), (32, 16, 16), (130, 5, 16), (21, 9, 8), (64, 70, 64), (300, 3, 32)])
 def test_keys_at_the_windows_edge_and_among_the_kept_first_decide(tmp_path, window, keep, page, dtype):
     """Attention whose last query finds one marked key above all others: the last logits are the marked token's when
     it sits just inside the window or is the last kept key, and show no trace of it just outside the window or just

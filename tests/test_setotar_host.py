@@ -93,7 +93,7 @@ def run(folder, steps, **options):
 LENGTHS = [5, 41, 1, 2, 23]
 
 
-@pytest.mark.parametrize("key", list(SETOTAR))
+@pytest.mark.parametrize("key", ["A", "B", "C", "D", "E"])
 def test_engine_with_stand_in_kernels_matches_plain(tmp_path, key):
     folder = make_setotar_folder(tmp_path, key)
     weights = read_weights(folder)
