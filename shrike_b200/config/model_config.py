@@ -322,7 +322,7 @@ class DecayLinearAttentionSpec(PartSpec):
 
 @dataclass(frozen=True)
 class GatedLinearRecurrenceSpec(PartSpec):
-    """Linear attention in which the forget gate also decides what is written (the HGRN2 cell).  Per head, with
+    """A linear recurrence with one gate for both ends (the HGRN2 cell): what a state row keeps, f, fixes what it takes in, 1 - f.  Per head, with
     q = silu(Wq x) (dim), v = Wv x (vdim) and the gate f = lower + (1 - lower) * sigmoid(Wf x + b) per channel of q:
 
         S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T  from S = 0;   o_t = S_t^T q_t   (no key, no scale)

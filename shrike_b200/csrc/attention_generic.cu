@@ -84,7 +84,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
   const size_t row_stride = static_cast<size_t>(num_kv_heads) * D;
 
   // with a window, the sequence's first `keep_first` keys stay visible after the window has passed them: they are
-  // walked first, at their true positions, then the window's own keys
+  // walked first, each at the position it has, then the window's own keys
   const int kept_end = window > 0 ? min(keep_first, first) : 0;
   for (int part = kept_end > 0 ? 0 : 1; part < 2; ++part) {
   const int part_first = part == 0 ? 0 : first, part_last = part == 0 ? kept_end - 1 : last;

@@ -1,4 +1,4 @@
-"""Linear attention in which the forget gate also decides what is written (the HGRN2 cell).
+"""A linear recurrence with one gate for both ends (the HGRN2 cell): what a state row keeps, f, fixes what it takes in, 1 - f.
 
 Per head, with q = silu(Wq x) (dim numbers), v = Wv x (vdim numbers) and a gate per channel of q,
 f = lower + (1 - lower) * sigmoid(Wf x + b):
